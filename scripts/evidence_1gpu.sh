@@ -19,12 +19,12 @@ PY
 done
 bash scripts/sweep_env.sh JLLAMA_MEGA_L2_AHEAD "0 8 16 32 48"
 python scripts/profile_run.py --mode prefill --layers 2 --steps 1 > gpurun_out/plain_prefill.log 2>&1 &&
-ncu --set full --clock-control none --import-source on -k regex:'gemm_kernel|flash_prefill|rmsnorm|rope_kv|embed' -c 14 \
+ncu --set full --clock-control none -k regex:'gemm_kernel|flash_prefill|rmsnorm|rope_kv|embed' -c 14 \
     -o gpurun_out/prof_prefill python scripts/profile_run.py --mode prefill --layers 2 --steps 1 > gpurun_out/ncu_prefill.log 2>&1
 python scripts/profile_run.py --mode decode --layers 4 --steps 2 > gpurun_out/plain_decode.log 2>&1 &&
-ncu --set full --clock-control none --import-source on -k regex:'decode_mega|mega_select|sample_full|argmax|advance' -c 6 \
+ncu --set full --clock-control none -k regex:'decode_mega|mega_select|sample_full|argmax|advance' -c 6 \
     -o gpurun_out/prof_decode python scripts/profile_run.py --mode decode --layers 4 --steps 2 > gpurun_out/ncu_decode.log 2>&1
 python scripts/profile_run.py --mode decode --layers 2 --steps 1 --batch 16 --prompt 512 > gpurun_out/plain_decode16.log 2>&1 &&
-ncu --set full --clock-control none --import-source on -k regex:'gemv|decode_attn|swiglu|sample_full' -c 12 \
+ncu --set full --clock-control none -k regex:'gemv|decode_attn|swiglu|sample_full' -c 12 \
     -o gpurun_out/prof_decode16 python scripts/profile_run.py --mode decode --layers 2 --steps 1 --batch 16 --prompt 512 > gpurun_out/ncu_decode16.log 2>&1
 ls -la gpurun_out/*.ncu-rep; tail -2 gpurun_out/ncu_prefill.log gpurun_out/ncu_decode.log gpurun_out/ncu_decode16.log
