@@ -35,6 +35,9 @@ struct PrepParams {
   const float* cos_t; const float* sin_t; int max_pos;      // [max_pos][rot/2]
   int unit_norm; float eps;
   const int* cache_len; const int* pad_left;
+  const float* bias;                // fp32, indexed like the columns of y (added before anything else), or nullptr
+  int v_norm;                       // values scaled to unit RMS per head (no weight) before they are cached
+  int v_token_major;                // value cache [B][T][G*Dv] (all heads of a token in one row) instead of [B][G][T][Dv]
 };
 
 constexpr int AP_WARPS = 4;      // heads per CTA of the preparation kernel (one warp each)
@@ -53,12 +56,21 @@ __global__ void __launch_bounds__(AP_WARPS * 32) attn_prep_kernel(PrepParams p, 
   const float* yr = p.y + (size_t)m * p.ldy;
   if (head >= p.H + p.G) {                               // value head: plain copy into the cache
     const int g = head - p.H - p.G;
-    T* dst = vc + (((size_t)b * p.G + g) * p.T + slot) * p.Dv;
-    for (int i = lane; i < p.Dv; i += 32) dst[i] = from_f<T>(yr[p.v_off + g * p.Dv + i]);
+    T* dst = p.v_token_major ? vc + (((size_t)b * p.T + slot) * p.G + g) * p.Dv : vc + (((size_t)b * p.G + g) * p.T + slot) * p.Dv;
+    const float* vb = p.bias ? p.bias + p.v_off + g * p.Dv : nullptr;
+    float r = 1.0f;
+    if (p.v_norm) {
+      float ss = 0.0f;
+      for (int i = lane; i < p.Dv; i += 32) { const float v = yr[p.v_off + g * p.Dv + i] + (vb ? vb[i] : 0.0f); ss += v * v; }
+      r = 1.0f / sqrtf(warp_sum(ss) / (float)p.Dv + p.eps);
+    }
+    for (int i = lane; i < p.Dv; i += 32) dst[i] = from_f<T>((yr[p.v_off + g * p.Dv + i] + (vb ? vb[i] : 0.0f)) * r);
     return;
   }
   const bool is_q = head < p.H;
-  const float* src = yr + (is_q ? p.q_off + head * p.D : p.k_off + (head - p.H) * p.D);
+  const int col = is_q ? p.q_off + head * p.D : p.k_off + (head - p.H) * p.D;
+  const float* src = yr + col;
+  const float* bs = p.bias ? p.bias + col : nullptr;
   T* dst = is_q ? q_out + ((size_t)m * p.H + head) * p.D
                 : kc + (((size_t)b * p.G + (head - p.H)) * p.T + slot) * p.D;
   const float* ct = p.cos_t + (size_t)pos * (p.rot / 2);
@@ -73,6 +85,7 @@ __global__ void __launch_bounds__(AP_WARPS * 32) attn_prep_kernel(PrepParams p, 
       float u, v;
       if (pair_loads) { const float2 t = *reinterpret_cast<const float2*>(src + c0); u = t.x; v = t.y; }
       else { u = src[c0]; v = c1 < p.D ? src[c1] : 0.0f; }
+      if (bs) { u += bs[c0]; if (c1 < p.D) v += bs[c1]; }
       if (c1 < p.rot) { const float c = ct[i], sn = st[i]; const float ru = u * c - v * sn, rv = v * c + u * sn; u = ru; v = rv; }
       if (pass == 0) {
         ss += u * u + v * v;
@@ -172,7 +185,19 @@ struct AttnParams {
   const int* cache_len;             // slots already filled BEFORE this call's tokens (device scalar); nullptr = 0
   const int* pad_left;
   const float* gate; int ldg;       // fp32 pre-activation of the per-head output gate (column h of row m), or nullptr
+  int sink;                         // 1: the softmax denominator has one more term exp(0) (a key with score 0 and no value)
+  float* out32;                     // fp32 output [M][H][Dv] instead of `out` (what a later fp32 step reads), or nullptr
 };
+
+// the denominator of a row whose running maximum is m and whose visible keys sum to l (l == 0: nothing visible, the row is zero)
+__device__ __forceinline__ float attn_inv_denominator(const AttnParams& p, float m, float l) {
+  if (!(l > 0.0f)) return 0.0f;
+  return 1.0f / (p.sink ? l + expf(-m) : l);
+}
+template <typename T>
+__device__ __forceinline__ void attn_store(const AttnParams& p, T* out, size_t at, float v) {
+  if (p.out32) p.out32[at] = v; else out[at] = from_f<T>(v);
+}
 
 constexpr int AT_MAXV = 16;         // value columns per lane: Dv <= 512
 
@@ -357,12 +382,12 @@ __global__ void __launch_bounds__(AR_WARPS * 32) attn_rows_kernel(AttnParams p, 
     const int s = q0 + warp * AR_QW + qi;
     if (s >= p.S) continue;
     const int m = b * p.S + s;
-    float gmul = lrun[qi] > 0.0f ? 1.0f / lrun[qi] : 0.0f;      // a padding query sees nothing: its row is zero
+    float gmul = attn_inv_denominator(p, mrun[qi], lrun[qi]);  // a padding query sees nothing: its row is zero
     if (p.gate) gmul *= sigmoid_f(p.gate[(size_t)m * p.ldg + h]);
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
       const int c = lane + 32 * i;
-      if (c < p.Dv) out[((size_t)m * p.H + h) * p.Dv + c] = from_f<T>(acc[qi][i] * gmul);
+      if (c < p.Dv) attn_store<T>(p, out, ((size_t)m * p.H + h) * p.Dv + c, acc[qi][i] * gmul);
     }
   }
 }
@@ -403,12 +428,12 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(AttnParams p
   for (int w = 0; w < AD_WARPS; ++w) mall = fmaxf(mall, ml[2 * w]);
   float lall = 0.0f;
   for (int w = 0; w < AD_WARPS; ++w) if (ml[2 * w] != -INFINITY) lall += ml[2 * w + 1] * expf(ml[2 * w] - mall);
-  float gmul = lall > 0.0f ? 1.0f / lall : 0.0f;
+  float gmul = attn_inv_denominator(p, mall, lall);
   if (p.gate) gmul *= sigmoid_f(p.gate[(size_t)b * p.ldg + h]);
   for (int c = threadIdx.x; c < p.Dv; c += blockDim.x) {
     float o = 0.0f;
     for (int w = 0; w < AD_WARPS; ++w) if (ml[2 * w] != -INFINITY) o += part[w * p.Dv + c] * expf(ml[2 * w] - mall);
-    out[((size_t)b * p.H + h) * p.Dv + c] = from_f<T>(o * gmul);
+    attn_store<T>(p, out, ((size_t)b * p.H + h) * p.Dv + c, o * gmul);
   }
 }
 
@@ -527,7 +552,7 @@ __global__ void attn_merge_kernel(AttnParams p, const float* __restrict__ part, 
   pdl_wait();                      // programmatic dependent launch: nothing is read before the predecessor is done
   pdl_launch_dependents();
   __shared__ float wz[64];                                 // weight of every split (splits <= 64)
-  __shared__ float tot;
+  __shared__ float tot, top;
   const int h = blockIdx.x, b = blockIdx.y;
   const float* src = part + ((size_t)b * p.H + h) * splits * (p.Dv + 2);
   if (threadIdx.x < 32) {                                  // the splits' maxima and sums, all loads at once
@@ -542,17 +567,17 @@ __global__ void attn_merge_kernel(AttnParams p, const float* __restrict__ part, 
     float lall = 0.0f;                                     // summed in split order, as the columns below are
     for (int zz = 0; zz < splits; ++zz)
       lall += zz < 32 ? __shfl_sync(0xffffffffu, l0 * w0, zz) : __shfl_sync(0xffffffffu, l1 * w1, zz - 32);
-    if (lane == 0) tot = lall;
+    if (lane == 0) { tot = lall; top = mall; }
   }
   __syncthreads();
   const float lall = tot;
-  float gmul = lall > 0.0f ? 1.0f / lall : 0.0f;
+  float gmul = attn_inv_denominator(p, top, lall);
   if (p.gate) gmul *= sigmoid_f(p.gate[(size_t)b * p.ldg + h]);
   for (int c = threadIdx.x; c < p.Dv; c += blockDim.x) {
     float o = 0.0f;
 #pragma unroll 8
     for (int zz = 0; zz < splits; ++zz) o = fmaf(src[(size_t)zz * (p.Dv + 2) + 2 + c], wz[zz], o);
-    out[((size_t)b * p.H + h) * p.Dv + c] = from_f<T>(o * gmul);
+    attn_store<T>(p, out, ((size_t)b * p.H + h) * p.Dv + c, o * gmul);
   }
 }
 
@@ -575,11 +600,12 @@ using namespace jl;
 extern "C" JL_API int jl_attn_prep(const float* y, int ldy, int q_off, int k_off, int v_off, void* q_out, void* k_cache,
                                    void* v_cache, const float* cos_t, const float* sin_t, int max_pos, int rot, int unit_norm,
                                    float eps, const int* cache_len, const int* pad_left, int B, int S, int H, int G, int D, int Dv,
-                                   int T_cap, int dtype, void* stream) {
+                                   int T_cap, const float* bias, int v_norm, int v_token_major, int dtype, void* stream) {
   JL_CHECK_ARG(B >= 1 && S >= 1 && H >= 1 && G >= 1 && D >= 1 && Dv >= 1, "jl_attn_prep: bad shape");
   JL_CHECK_ARG(rot >= 0 && rot <= D && rot % 2 == 0, "jl_attn_prep: rot=%d must be even and <= D=%d", rot, D);
   JL_CHECK_ARG(k_off >= 0 || (k_cache == nullptr && v_cache == nullptr), "jl_attn_prep: queries-only call takes no caches");
-  PrepParams p{y, ldy, q_off, k_off, v_off, B, S, H, G, D, Dv, T_cap, rot, cos_t, sin_t, max_pos, unit_norm, eps, cache_len, pad_left};
+  PrepParams p{y, ldy, q_off, k_off, v_off, B, S, H, G, D, Dv, T_cap, rot, cos_t, sin_t, max_pos, unit_norm, eps, cache_len, pad_left,
+               bias, v_norm, v_token_major};
   const int n_heads = k_off >= 0 ? H + 2 * G : H;
   const int pair_loads = D % 2 == 0 && ldy % 2 == 0 && q_off % 2 == 0 && (k_off < 0 || k_off % 2 == 0) && (uintptr_t)y % 8 == 0;
   dim3 grid(B * S, (n_heads + AP_WARPS - 1) / AP_WARPS);
@@ -602,13 +628,14 @@ extern "C" JL_API int jl_attn_generic_splits(int B, int H, int G, int T_cap) {
 static int attn_launch(const void* q, const void* k_cache, const void* v_cache, void* out, const float* gate, int ldg,
                        const int* cache_len, const int* pad_left, int B, int S, int H, int G, int D, int Dv, int T_cap, int ldk,
                        int ldv, int window, float scale, float* scratch, int splits, int dtype, void* stream,
-                       long long k_bs = 0, long long k_hs = 0, long long v_bs = 0, long long v_hs = 0) {
+                       long long k_bs = 0, long long k_hs = 0, long long v_bs = 0, long long v_hs = 0, int sink = 0,
+                       float* out32 = nullptr) {
   JL_CHECK_ARG(B >= 1 && S >= 1 && G >= 1 && H % G == 0, "jl_attn_generic: H=%d not a multiple of G=%d", H, G);
   JL_CHECK_ARG(Dv <= 32 * AT_MAXV, "jl_attn_generic: value size %d above %d", Dv, 32 * AT_MAXV);
   JL_CHECK_ARG(ldk >= D && ldv >= Dv && window >= 0, "jl_attn_generic: bad pitch %d / %d or window %d", ldk, ldv, window);
   if (k_bs == 0 && k_hs == 0) { k_hs = (long long)T_cap * ldk; k_bs = k_hs * G; }
   if (v_bs == 0 && v_hs == 0) { v_hs = (long long)T_cap * ldv; v_bs = v_hs * G; }
-  AttnParams p{B, S, H, G, D, Dv, T_cap, ldk, ldv, k_bs, k_hs, v_bs, v_hs, window, scale, cache_len, pad_left, gate, ldg};
+  AttnParams p{B, S, H, G, D, Dv, T_cap, ldk, ldv, k_bs, k_hs, v_bs, v_hs, window, scale, cache_len, pad_left, gate, ldg, sink, out32};
   cudaStream_t st = (cudaStream_t)stream;
   if (S == 1 && scratch != nullptr && splits >= 1 && splits <= 64) {
     const int dp = ((D + 3) & ~3) + 4;
@@ -660,9 +687,10 @@ extern "C" JL_API int jl_attn_generic(const void* q, const void* k_cache, const 
 extern "C" JL_API int jl_attn_windowed(const void* q, const void* k_cache, const void* v_cache, void* out, const int* cache_len,
                                        const int* pad_left, int B, int S, int H, int G, int D, int Dv, int T_cap, int ldk, int ldv,
                                        long long k_bs, long long k_hs, long long v_bs, long long v_hs, int window, float scale,
-                                       float* scratch, int splits, int dtype, void* stream) {
+                                       float* scratch, int splits, int sink, float* out32, int dtype, void* stream) {
+  JL_CHECK_ARG(out != nullptr || out32 != nullptr, "jl_attn_windowed: no output");
   return attn_launch(q, k_cache, v_cache, out, nullptr, 0, cache_len, pad_left, B, S, H, G, D, Dv, T_cap, ldk, ldv, window, scale,
-                     scratch, splits, dtype, stream, k_bs, k_hs, v_bs, v_hs);
+                     scratch, splits, dtype, stream, k_bs, k_hs, v_bs, v_hs, sink, out32);
 }
 
 extern "C" JL_API int jl_latent_prep(const float* y, int ldy, int q_off, int q_rank, int kv_off, int kv_rank, int rot_dim, int rot,

@@ -44,15 +44,25 @@ struct GlaParams {
   const float* head_decay;             // [H] fp32, or nullptr: alpha from the low-rank projection
   const float* cos_t; const float* sin_t; int rot, layout, max_pos;      // tables [max_pos][rot/2]; rot == 0: no rotation
   float k_scale;
+  // state space scan (jl_ssd_scan): q / k are shared by the qk_div heads of a group; the decay of (token, head) is
+  // aux[m * ld_aux + h] and the value row is scaled by aux[m * ld_aux + H + h]
+  int qk_div;                          // heads per q / k head (1: every head has its own)
+  const float* aux; int ld_aux;
 };
+
+__device__ __forceinline__ float scan_value_scale(const GlaParams& p, size_t m, int h) {
+  return p.aux ? p.aux[m * p.ld_aux + p.H + h] : 1.0f;
+}
 
 // q, k and alpha of channel d of head h for the token whose projection row is yr (position pos).
 template <typename T>
-__device__ __forceinline__ void scan_channel(const GlaParams& p, const float* __restrict__ yr, int h, int d, int pos,
+__device__ __forceinline__ void scan_channel(const GlaParams& p, size_t m, int h, int d, int pos,
                                              const float* __restrict__ zs, const T* __restrict__ a2, const T* __restrict__ a2b,
                                              float& qv, float& kv, float& av) {
-  const float* qh = yr + p.q_off + h * p.D;
-  const float* kh = yr + p.k_off + h * p.D;
+  const float* yr = p.y + m * p.ldy;
+  const int hq = p.qk_div > 1 ? h / p.qk_div : h;
+  const float* qh = yr + p.q_off + hq * p.D;
+  const float* kh = yr + p.k_off + hq * p.D;
   if (p.rot > 0) {
     const float* ct = p.cos_t + (size_t)pos * (p.rot / 2);
     const float* st = p.sin_t + (size_t)pos * (p.rot / 2);
@@ -62,6 +72,7 @@ __device__ __forceinline__ void scan_channel(const GlaParams& p, const float* __
     qv = qh[d] * p.q_scale;
     kv = kh[d] * p.k_scale;
   }
+  if (p.aux) { av = p.aux[m * p.ld_aux + h]; return; }
   if (p.head_decay) { av = p.head_decay[h]; return; }
   const int n = h * p.D + d;
   float z = to_f(a2b[n]);
@@ -112,7 +123,8 @@ __global__ void __launch_bounds__(GS_THREADS, 3) gla_scan_kernel(GlaParams p, co
     }
     for (int i = tid; i < nt * cols; i += GS_THREADS) {
       const int t = i / cols, c = blockIdx.x * cols + i % cols;
-      vs[i] = c < p.Dv ? p.y[(size_t)(b * p.S + s0 + t) * p.ldy + p.v_off + h * p.Dv + c] : 0.0f;
+      const size_t mt = (size_t)(b * p.S + s0 + t);
+      vs[i] = c < p.Dv ? p.y[mt * p.ldy + p.v_off + h * p.Dv + c] * scan_value_scale(p, mt, h) : 0.0f;
     }
     __syncthreads();
     for (int i = tid; i < nt * P * GS_DP; i += GS_THREADS) {
@@ -120,8 +132,7 @@ __global__ void __launch_bounds__(GS_THREADS, 3) gla_scan_kernel(GlaParams p, co
       const int at = t * DS + (d / GS_DP) * GS_PITCH + d % GS_DP;
       float qv = 0.0f, kv = 0.0f, av = 1.0f;
       if (d < p.D)
-        scan_channel<T>(p, p.y + (size_t)(b * p.S + s0 + t) * p.ldy, h, d, scan_position(p, b, s0 + t), zs + t * p.R, a2, a2b,
-                        qv, kv, av);
+        scan_channel<T>(p, (size_t)(b * p.S + s0 + t), h, d, scan_position(p, b, s0 + t), zs + t * p.R, a2, a2b, qv, kv, av);
       qs[at] = qv; ks[at] = kv; as[at] = av;
     }
     __syncthreads();
@@ -195,14 +206,14 @@ __global__ void __launch_bounds__(128) gla_prep_kernel(GlaParams p, const T* __r
   for (int i = threadIdx.x; i < p.H * per_head; i += blockDim.x) {
     const int h = i / per_head, d = i % per_head;
     float qv = 0.0f, kv = 0.0f, av = 1.0f;
-    if (d < p.D) scan_channel<T>(p, yr, h, d, pos, zs, a2, a2b, qv, kv, av);
+    if (d < p.D) scan_channel<T>(p, (size_t)m, h, d, pos, zs, a2, a2b, qv, kv, av);
     float* o = out + (size_t)h * RF + (d / DP) * pitch + d % DP;
     o[0] = qv; o[P * pitch] = kv; o[2 * P * pitch] = av;
   }
   const int dvp = (p.Dv + 3) & ~3;
   for (int i = threadIdx.x; i < p.H * dvp; i += blockDim.x) {
     const int h = i / dvp, c = i % dvp;
-    out[(size_t)h * RF + 3 * P * pitch + c] = c < p.Dv ? yr[p.v_off + h * p.Dv + c] : 0.0f;
+    out[(size_t)h * RF + 3 * P * pitch + c] = c < p.Dv ? yr[p.v_off + h * p.Dv + c] * scan_value_scale(p, (size_t)m, h) : 0.0f;
   }
 }
 
@@ -446,5 +457,16 @@ extern "C" JL_API int jl_retention_scan(const float* y, int ldy, int q_off, int 
   GlaParams p{y, ldy, q_off, k_off, v_off, 0, B, S, H, D, Dv, 0, 1, q_scale, 1.0f, cache_len, pad_left, state, o};
   p.head_decay = head_decay; p.cos_t = cos_t; p.sin_t = sin_t; p.rot = rot; p.layout = layout; p.max_pos = max_pos;
   p.k_scale = k_scale;
+  return launch_scan(p, nullptr, nullptr, ws, DT_F32, stream);
+}
+
+extern "C" JL_API int jl_ssd_scan(const float* u, int ldu, int q_off, int k_off, int v_off, int G, const float* aux, float* state,
+                                  float* o, const int* cache_len, const int* pad_left, int B, int S, int H, int D, int Dv,
+                                  float* ws, void* stream) {
+  JL_CHECK_ARG(B >= 1 && S >= 1 && H >= 1 && D >= 1 && Dv >= 1 && aux != nullptr, "jl_ssd_scan: bad shape");
+  JL_CHECK_ARG(G >= 1 && H % G == 0, "jl_ssd_scan: %d heads in %d groups", H, G);
+  GlaParams p{u, ldu, q_off, k_off, v_off, 0, B, S, H, D, Dv, 0, 1, 1.0f, 1.0f, cache_len, pad_left, state, o};
+  p.k_scale = 1.0f;
+  p.qk_div = H / G; p.aux = aux; p.ld_aux = 2 * H;
   return launch_scan(p, nullptr, nullptr, ws, DT_F32, stream);
 }

@@ -23,6 +23,7 @@ struct RouteParams {
   int score, normalise;
   float scale;
   int* idx; float* wt;              // [M][top]
+  const float* bias;                // [E] fp32 added to the logits, or nullptr
 };
 
 constexpr int RT_WARPS = 4;
@@ -48,16 +49,17 @@ __global__ void __launch_bounds__(RT_WARPS * 32) moe_route_kernel(RouteParams p)
   float* work = s + p.E;
   float* gs = work + p.E;
   const float* zr = p.z + (size_t)m * p.ldz;
+  auto logit = [&](int e) { return p.bias ? zr[e] + p.bias[e] : zr[e]; };
   if (p.score == SCORE_SOFTMAX) {
     float mx = -INFINITY;
-    for (int e = lane; e < p.E; e += 32) mx = fmaxf(mx, zr[e]);
+    for (int e = lane; e < p.E; e += 32) mx = fmaxf(mx, logit(e));
     mx = warp_max(mx);
     float sum = 0.0f;
-    for (int e = lane; e < p.E; e += 32) { const float v = expf(zr[e] - mx); s[e] = v; sum += v; }
+    for (int e = lane; e < p.E; e += 32) { const float v = expf(logit(e) - mx); s[e] = v; sum += v; }
     sum = warp_sum(sum);
     for (int e = lane; e < p.E; e += 32) s[e] = s[e] / sum;
   } else {
-    for (int e = lane; e < p.E; e += 32) s[e] = sigmoid_f(zr[e]);
+    for (int e = lane; e < p.E; e += 32) s[e] = sigmoid_f(logit(e));
   }
   __syncwarp();
   for (int e = lane; e < p.E; e += 32) work[e] = s[e];
@@ -186,12 +188,12 @@ __global__ void __launch_bounds__(128) moe_gather_kernel(const T* __restrict__ x
 using namespace jl;
 
 extern "C" JL_API int jl_moe_route(const float* z, int ldz, int M, int E, int top, int groups, int keep, int group_top, int score,
-                                   int normalise, float scale, int* idx, float* wt, void* stream) {
+                                   int normalise, float scale, const float* bias, int* idx, float* wt, void* stream) {
   JL_CHECK_ARG(M >= 1 && E >= 1 && top >= 1 && top <= E && ldz >= E, "jl_moe_route: bad shape M=%d E=%d top=%d ldz=%d", M, E, top, ldz);
   JL_CHECK_ARG(groups <= 1 || (E % groups == 0 && keep >= 1 && keep <= groups && group_top >= 1 && keep * (E / groups) >= top),
                "jl_moe_route: %d groups of %d experts, keep %d, cannot give %d choices", groups, groups > 0 ? E / groups : 0, keep, top);
   JL_CHECK_ARG(score == SCORE_SIGMOID || score == SCORE_SOFTMAX, "jl_moe_route: score function %d", score);
-  RouteParams p{z, ldz, M, E, top, groups, keep, group_top, score, normalise, scale, idx, wt};
+  RouteParams p{z, ldz, M, E, top, groups, keep, group_top, score, normalise, scale, idx, wt, bias};
   const size_t smem = (size_t)RT_WARPS * (2 * E + (groups > 1 ? groups : 0)) * sizeof(float);
   JL_CHECK_ARG(smem <= 200 * 1024, "jl_moe_route: %d experts do not fit shared memory", E);
   if (smem > 48 * 1024) JL_CUDA(cudaFuncSetAttribute(moe_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

@@ -206,7 +206,7 @@ extern "C" JL_API int jl_linear_any(const void* x, int ldx, const void* w, void*
                                     float p0, float p1, int dtype, int out_f32, void* stream) {
   JL_CHECK_ARG(M >= 1 && N >= 1 && K >= 1 && ldx >= K && ldo >= N, "jl_linear_any: bad shape M=%d N=%d K=%d ldx=%d ldo=%d", M, N,
                K, ldx, ldo);
-  JL_CHECK_ARG(act >= 0 && act <= ACT_SCALE_SOFTCAP, "jl_linear_any: bad activation %d", act);
+  JL_CHECK_ARG(act >= 0 && act <= ACT_SIGMOID, "jl_linear_any: bad activation %d", act);
   cudaStream_t st = (cudaStream_t)stream;
   int rc;
   if (dtype == DT_BF16)
@@ -226,7 +226,7 @@ extern "C" JL_API int jl_linear_grouped(const void* x, int ldx, long long x_bs, 
                                         void* stream) {
   JL_CHECK_ARG(M >= 1 && N >= 1 && K >= 1 && ldx >= K && ldo >= N && nbatch >= 1 && x_div >= 1, "jl_linear_grouped: bad shape M=%d N=%d K=%d ldx=%d ldo=%d",
                M, N, K, ldx, ldo);
-  JL_CHECK_ARG(act >= 0 && act <= ACT_SCALE_SOFTCAP, "jl_linear_grouped: bad activation %d", act);
+  JL_CHECK_ARG(act >= 0 && act <= ACT_SIGMOID, "jl_linear_grouped: bad activation %d", act);
   JL_CHECK_ARG(tile_group == nullptr || M % LT_BM == 0, "jl_linear_grouped: sorted rows come in tiles of %d, M=%d", LT_BM, M);
   JL_CHECK_ARG(nbatch <= 65535, "jl_linear_grouped: %d batches above the grid limit", nbatch);
   cudaStream_t st = (cudaStream_t)stream;

@@ -11,7 +11,7 @@ namespace jl {
 
 enum { DT_BF16 = 0, DT_F32 = 1 };
 // epilogue / activation codes shared by the generic linears and jl_act_cast
-enum { ACT_NONE = 0, ACT_RELU2 = 1, ACT_GELU_TANH = 2, ACT_SILU = 3, ACT_SCALE_SOFTCAP = 4 };
+enum { ACT_NONE = 0, ACT_RELU2 = 1, ACT_GELU_TANH = 2, ACT_SILU = 3, ACT_SCALE_SOFTCAP = 4, ACT_SIGMOID = 5 };
 
 __device__ __forceinline__ float to_f(float v) { return v; }
 __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
@@ -26,6 +26,7 @@ __device__ __forceinline__ float apply_act(float z, int act, float p0, float p1)
     case ACT_RELU2: { float r = fmaxf(z, 0.0f); return r * r; }
     case ACT_GELU_TANH: return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
     case ACT_SILU: return z * sigmoid_f(z);
+    case ACT_SIGMOID: return sigmoid_f(z);
     case ACT_SCALE_SOFTCAP: { float s = z * p0; return p1 > 0.0f ? p1 * tanhf(s / p1) : s; }
     default: return z;
   }

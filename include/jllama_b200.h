@@ -286,7 +286,10 @@ int jl_linear_any(const void* x, int ldx, const void* w, void* out, int ldo, int
  * q at q_off ([H*D]), k at k_off ([G*D]; < 0: queries only), v at v_off ([G*Dv]); caches [B][G][T_cap][D|Dv] of dtype. */
 int jl_attn_prep(const float* y, int ldy, int q_off, int k_off, int v_off, void* q_out, void* k_cache, void* v_cache,
                  const float* cos_t, const float* sin_t, int max_pos, int rot, int unit_norm, float eps, const int* cache_len,
-                 const int* pad_left, int B, int S, int H, int G, int D, int Dv, int T_cap, int dtype, void* stream);
+                 const int* pad_left, int B, int S, int H, int G, int D, int Dv, int T_cap, const float* bias, int v_norm,
+                 int v_token_major, int dtype, void* stream);
+/* (jl_attn_prep) bias: fp32 indexed like the columns of y, added first (NULL: none); v_norm: values scaled to unit RMS per head
+ * before they are cached; v_token_major: value cache [B][T_cap][G*Dv] instead of [B][G][T_cap][Dv]. */
 /* Causal softmax attention of S new tokens per row (slots *cache_len .. *cache_len+S-1) over slots [pad_left[b], own slot];
  * q [B*S, H, D], out [B*S, H, Dv]; gate (optional) fp32 [B*S, ldg], column h: out *= sigmoid(gate).
  * One new token (S == 1) with `scratch` (B*H*splits*(Dv+2) floats, splits from jl_attn_generic_splits, at most 64): the keys
@@ -329,7 +332,9 @@ int jl_linear_grouped(const void* x, int ldx, long long x_bs, const void* w, lon
 int jl_attn_windowed(const void* q, const void* k_cache, const void* v_cache, void* out, const int* cache_len,
                      const int* pad_left, int B, int S, int H, int G, int D, int Dv, int T_cap, int ldk, int ldv,
                      long long k_bs, long long k_hs, long long v_bs, long long v_hs, int window, float scale, float* scratch,
-                     int splits, int dtype, void* stream);
+                     int splits, int sink, float* out32, int dtype, void* stream);
+/* (jl_attn_windowed) sink: the softmax denominator has one more term exp(0) — a key with score 0 that carries no value;
+ * out32: fp32 output [B*S, H, Dv] written instead of `out`. */
 /* Latent attention, preparation.  y fp32 [B*S, ldy] holds the query latent (q_rank columns at q_off; 0: none) and the key /
  * value latent followed by the rotated key part shared by the heads (kv_rank + rot_dim columns at kv_off).  The latents are
  * RMS-normed with plain weights; the key part is rotated on its first `rot` channels.  cq [B*S, q_rank]; cache
@@ -349,7 +354,8 @@ int jl_rotary_slice(const void* in, int ldi, int in_hs, int in_off, void* out, i
  * of the `keep` best groups can be chosen.  idx int32 / wt fp32 [M, top]: the top largest, weights = scores (over their sum
  * + 1e-20 when normalise) * scale. */
 int jl_moe_route(const float* z, int ldz, int M, int E, int top, int groups, int keep, int group_top, int score, int normalise,
-                 float scale, int* idx, float* wt, void* stream);
+                 float scale, const float* bias, int* idx, float* wt, void* stream);
+/* (jl_moe_route) bias: fp32 [E] added to the logits (NULL: none). */
 /* Order the M * top (token, choice) pairs by expert into segments rounded up to `tile` rows (cap >= jl_moe_sorted_rows rows):
  * pos [M * top]: row of each pair; row_src [cap]: token of each row (-1: padding); tile_group [cap / tile]: expert (-1: none);
  * tiles_used (optional): the number of leading tiles that belong to an expert. */
@@ -366,6 +372,55 @@ int jl_moe_gather(const void* x, int ldx, const int* row_src, void* xs, int rows
  * tiles_used (optional, device int): only that many leading tiles are computed. */
 int jl_gemm_grouped(const void* x, const void* w, void* out, int M, int N, int K, int groups, const int* tile_group,
                     const int* tiles_used, int out_f32, int num_sms, void* stream);
+
+/* ---- token embedding with a hashed pair table, short convolutions with state, delta-rule and state-space scans,
+ *      gated activations and the norms around mixers that run side by side (csrc/seq_mix.cu, delta_scan.cu, gla_scan.cu) */
+
+/* out[m] = norm(table[id] + pair[r]) * norm_w (fp32 [B*S, W]; norm_w NULL: no norm), r = (prev * mul_prev + id * mul_cur) mod
+ * buckets with prev the token before it in its sequence, r = buckets for a sequence's first token (position
+ * *cache_len + s - pad_left[b] == 0); rows at negative positions are zero.  prev_tok int32 [B]: the last token of the
+ * previous call, replaced by this call's last. */
+int jl_embed_pair_norm(const int* ids, const void* table, const void* pair, const void* norm_w, float* out, int* prev_tok,
+                       const int* cache_len, const int* pad_left, int B, int S, int W, int V, int buckets, long long mul_prev,
+                       long long mul_cur, float eps, int dtype, void* stream);
+/* Causal convolution over time per channel: out[m, c] = act(bias[c] + sum_j w[c][taps-1-j] * in[token - j][c]), inputs fp32
+ * columns col0 .. col0+C-1 of y, zeros before a sequence's start; state fp32 [B][taps-1][C] holds the last taps-1 inputs of
+ * every row (read for the first tokens of the call, replaced by the call's last inputs).  w [C][taps], bias [C] or NULL. */
+int jl_causal_conv(const float* y, int ldy, int col0, int C, const void* w, const void* bias, float* state, float* out, int ldo,
+                   const int* cache_len, const int* pad_left, int B, int S, int taps, int act, int dtype, void* stream);
+/* out[m] = c * (norm(a[m]) * wa + norm(b[m]) * wb), fp32 [M, W] (b NULL: one branch). */
+int jl_norm_mean2(const float* a, int lda, const void* wa, const float* b, int ldb, const void* wb, float c, float* out, int M,
+                  int W, float eps, int dtype, void* stream);
+/* out[m, i] = norm_group((o[m, i] + skip[i / P] * x[m, i]) * act(z[m, i])) * w[i]: the gate first, then an RMS norm over each
+ * of `groups` equal parts of the N = H * P columns.  skip [H] and x may be NULL. */
+int jl_gated_groupnorm(const float* o, const float* x, int ldx, const void* skip, int P, const float* z, int ldz, const void* w,
+                       void* out, int M, int N, int groups, float eps, int gate_act, int dtype, void* stream);
+/* Gated activation of a fused gate | up product: out[m, j] = f(in[m, g_off + j], in[m, u_off + j]).  kind 0: act(g) * u;
+ * kind 1: g' = min(g, limit), u' = clamp(u, -limit, limit), g' * sigmoid(alpha * g') * (u' + 1).  With the device counter
+ * rows_used only the first *rows_used * rows_mult rows are computed. */
+int jl_glu_act(const float* in, int ldi, int g_off, int u_off, void* out, int ldo, int M, int F, int kind, int act, float limit,
+               float alpha, const int* rows_used, int rows_mult, int dtype, void* stream);
+/* Mixing of attention weights across heads, applied after the weighted sums: o fp32 [M][H][Gc][Dv] holds, for query head g
+ * and key/value head c0 + c, sum_j weight_g(j) v_c(j); out[m, h, :] = sum_g mix[h][g] * o[m, g, kv(h) - c0, :] for the heads
+ * whose key/value head kv(h) = h / (H / G) lies in [c0, c0 + Gc). */
+int jl_talk_mix(const float* o, const void* mix, void* out, int M, int H, int G, int Gc, int c0, int Dv, int dtype, void* stream);
+/* Per token and head of a selective state space layer: dt = softplus(y[m, dt_off + h] + dt_bias[h]),
+ * aux[m, h] = exp(-exp(A_log[h]) * dt), aux[m, H + h] = dt  (fp32 [M, 2H]). */
+int jl_ssd_gates(const float* y, int ldy, int dt_off, const void* dt_bias, const void* a_log, float* aux, int M, int H, int dtype,
+                 void* stream);
+/* State space scan on the gated-linear-attention kernels: S_t = aux[t, h] S_(t-1) + (aux[t, H + h] v_t) k_t^T, o_t = S_t^T q_t,
+ * q / k shared by the H / G heads of a group (columns q_off + g * D ...), v [H * Dv]; state fp32 [B, H, D, Dv]. */
+int jl_ssd_scan(const float* u, int ldu, int q_off, int k_off, int v_off, int G, const float* aux, float* state, float* o,
+                const int* cache_len, const int* pad_left, int B, int S, int H, int D, int Dv, float* ws, void* stream);
+/* Gated delta rule with one decay per key channel, per head: S <- diag(a_t) S; e = beta_t (v_t - S^T k_t); S <- S + k_t e^T;
+ * o_t = S^T q_t.  u fp32 [M, ldu]: q, k (G heads of D, after their convolutions) and v (H heads of Dv); q and k are scaled to
+ * unit length per head (1e-6 inside the root), q also by D^(-1/2).  y fp32 [M, ldy]: beta logits (H columns at b_off) and
+ * the rank-R decay input (a_off); a_t = exp(-exp(a_log[h]) * softplus(a2 (.) + a_bias)), a2 [H*D, R], a_bias [H*D].
+ * state fp32 [B, H, D, Dv]; o fp32 [M, H*Dv]; ws: jl_delta_scan_ws_floats floats. */
+size_t jl_delta_scan_ws_floats(int B, int S, int H, int D, int Dv);
+int jl_delta_scan(const float* u, int ldu, int q_off, int k_off, int v_off, int G, const float* y, int ldy, int b_off, int a_off,
+                  const void* a2, const void* a_bias, const void* a_log, float* state, float* o, const int* cache_len,
+                  const int* pad_left, int B, int S, int H, int D, int Dv, int R, float* ws, int dtype, void* stream);
 
 #ifdef __cplusplus
 }

@@ -288,6 +288,11 @@ class AttentionMixerSpec:
     kv_from: Optional[int] = None
     qk_unit_norm: bool = True
     head_gate: bool = True
+    bias: bool = False              # q / k / v projections have biases (`<name>.b`)
+    v_unit_norm: bool = False       # every head's value scaled to unit RMS (no weight) before it is cached
+    window: int = 0                 # > 0: a query sees itself and the window - 1 tokens before it
+    sink: bool = False              # one more unit in the softmax denominator: a key with score 0 that carries no value
+    talking_heads: bool = False     # the heads' weights are mixed by `talk` [heads, heads] after the softmax
     kind: str = "attention"
 
 
@@ -332,9 +337,58 @@ class RetentionMixerSpec:
 
 
 @dataclass
+class StateSpaceMixerSpec:
+    """Selective state space layer (state space duality form): per head a state [state x vdim] with one scalar decay per
+    token, S_t = exp(-exp(A_log) dt_t) S_(t-1) + dt_t B_t x_tᵀ, y_t = S_tᵀ C_t + D x_t; B and C shared by the heads of a
+    group; x, B, C through a causal convolution of `conv` taps and silu; the read-out gated by silu(z), then RMS-normed in
+    `norm_groups` equal parts."""
+    heads: int
+    vdim: int
+    state: int
+    groups: int = 1
+    conv: int = 4
+    norm_groups: int = 1
+    kind: str = "state_space"
+
+
+@dataclass
+class DeltaMixerSpec:
+    """Gated delta rule with one decay per key channel: S <- diag(a) S; e = beta (v - Sᵀk); S <- S + k eᵀ; o = Sᵀq.
+    q / k heads (kv_heads of `dim`) shared by groups of value heads, each of q, k, v through a causal convolution of
+    `conv` taps and silu, q and k scaled to unit length; read-out normed per head and gated by a low-rank sigmoid gate."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    conv: int = 4
+    kind: str = "channel_delta"
+
+
+@dataclass
+class ParallelMixerSpec:
+    """Two mixers side by side on the same input; each result is RMS-normed over the model width with its own weight and
+    the mixer returns `scale` times their sum."""
+    left: Any
+    right: Any
+    scale: float = 0.5
+    kind: str = "parallel"
+
+
+@dataclass
+class PairEmbeddingSpec:
+    """A second embedding table indexed by a hash of (previous token, token): row (prev * mul_prev + tok * mul_cur) mod
+    buckets, and row `buckets` for a sequence's first token."""
+    buckets: int
+    mul_prev: int
+    mul_cur: int
+
+
+@dataclass
 class DenseMlpSpec:
+    """down(act(up h)), or with `gated` down(act(gate h) * (up h))."""
     ff: int
     act: str = "relu2"
+    gated: bool = False
     kind: str = "dense"
 
 
@@ -356,6 +410,10 @@ class MoeMlpSpec:
     normalise: bool = True
     shared_ff: int = 0
     shared_gate: bool = True
+    gated: bool = False             # experts with a gate projection: act "glu_clamped" is min(g, limit) sigmoid(1.702 ·) (clamp(u) + 1)
+    limit: float = 0.0
+    shared_limit: float = 0.0
+    router_bias: bool = False       # `router.b` is added to the router logits
     kind: str = "moe"
 
 
@@ -372,6 +430,9 @@ class HybridConfig:
 
     * ``block``: "sandwich" — mixer and feed-forward one after the other, each between a norm before and a norm after,
       x += norm(sublayer(norm(x))); "parallel" — both read norms of the same x, x += residual_mult · (mixer + ff);
+      "parallel_shared" — the same with ONE norm that both sublayers read;
+    * ``tied_head``: the logits are taken against the embedding table (no ``head`` tensor); ``embed_norm``: a norm
+      (``embed.norm``) right after the embedding;
     * ``norm_offset``: what is added to a stored norm weight (1 for weights stored around zero);
     * which mixer types and feed-forward kinds it has (`_parse_mixer`, `_parse_mlp`)."""
 
@@ -380,16 +441,21 @@ class HybridConfig:
     block = "sandwich"
     norm_offset = 0.0
     default_eps = 1e-6
+    tied_head = False
+    embed_norm = False
 
     def __init__(self, vocab: int, width: int, layers: Any, norm: Optional[Dict[str, Any]] = None,
                  logit_scale: float = 1.0, logit_softcap: Optional[float] = None, residual_mult: float = 1.0,
-                 **extra: Any):
+                 embedding: Optional[Dict[str, Any]] = None, **extra: Any):
         self.vocab_size = int(vocab)
         self.hidden_size = int(width)
         self.rms_norm_eps = float((norm or {}).get("eps", self.default_eps))
         self.logit_scale = float(logit_scale)
         self.logit_softcap = float(logit_softcap) if logit_softcap else 0.0
         self.residual_mult = float(residual_mult)
+        self.embedding_dict = copy.deepcopy(embedding) if embedding else None
+        bg = (embedding or {}).get("bigram")
+        self.pair_embedding = PairEmbeddingSpec(int(bg["buckets"]), int(bg["mul_prev"]), int(bg["mul_cur"])) if bg else None
         self.layer_dicts = copy.deepcopy(list(layers))
         self.layers = [HybridLayerSpec(mixer=self._parse_mixer(i, d), mlp=self._parse_mlp(i, d.get("mlp")))
                        for i, d in enumerate(self.layer_dicts)]
@@ -425,6 +491,8 @@ class HybridConfig:
     def to_dict(self) -> Dict[str, Any]:
         d: Dict[str, Any] = {"architecture": self.architecture, "vocab": self.vocab_size, "width": self.hidden_size,
                              "norm": {"eps": self.rms_norm_eps}, "layers": copy.deepcopy(self.layer_dicts)}
+        if self.embedding_dict:
+            d["embedding"] = copy.deepcopy(self.embedding_dict)
         d.update(self._own_keys())
         d.update(self.extra)
         return d
@@ -567,3 +635,80 @@ class NikonexConfig(HybridConfig):
 
     def _own_keys(self) -> Dict[str, Any]:
         return {"residual_mult": self.residual_mult}
+
+
+class BazulornConfig(HybridConfig):
+    """Bazulorn: a decoder of parallel blocks with ONE norm per block — ``x += mixer(norm1 x) + ff(norm1 x)`` — whose token
+    embedding adds a row of a hashed (previous token, token) table and is normed, and whose logits are taken against the
+    embedding table.  Mixers: "parallel" — softmax attention (q / k / v biases, no rotation, unit-RMS values, sliding window,
+    a sink in the softmax denominator, weights mixed across heads) beside a selective state space layer, each result normed
+    over the model width, half their sum — and "channel_delta", a gated delta rule with one decay per key channel.
+    Feed-forward: a gated tanh-gelu layer or a mixture of clamped gated experts (biased router, softmax over the chosen
+    logits) plus a shared expert.
+
+    ``config.json``: ``vocab``, ``width``, ``norm.eps``, ``embedding.bigram.{buckets, mul_prev, mul_cur}`` and ``layers[i]`` =
+    ``{type, mixer, mlp}`` with, for "parallel", ``mixer.left.{heads, kv_heads, dim, vdim, scale, mask.size}`` and
+    ``mixer.right.{heads, vdim, state, groups, conv, norm_groups}``; for "channel_delta", ``mixer.{heads, kv_heads, dim, vdim,
+    conv}``; ``mlp`` null, ``{kind: dense, ff}`` or ``{kind: moe, router.{experts, top}, expert.{ff, limit}, shared.{ff, limit}}``."""
+
+    model_type = "bazulorn"
+    architecture = "Bazulorn"
+    block = "parallel_shared"
+    norm_offset = 0.0
+    tied_head = True
+    embed_norm = True
+
+    def _parse_mixer(self, i: int, d: Dict[str, Any]) -> Any:
+        m = d["mixer"]
+        kind = d["type"]
+        if kind == "parallel":
+            a, r = m["left"], m["right"]
+            left = AttentionMixerSpec(
+                heads=int(a["heads"]), kv_heads=int(a.get("kv_heads", a["heads"])), dim=int(a["dim"]), vdim=int(a["vdim"]),
+                scale=float(a["scale"]), rot=None, kv_from=None, qk_unit_norm=False, head_gate=False, bias=True,
+                v_unit_norm=True, window=int((a.get("mask") or {}).get("size") or 0), sink=True, talking_heads=True)
+            right = StateSpaceMixerSpec(heads=int(r["heads"]), vdim=int(r["vdim"]), state=int(r["state"]),
+                                        groups=int(r.get("groups", 1)), conv=int(r["conv"]),
+                                        norm_groups=int(r.get("norm_groups", 1)))
+            return ParallelMixerSpec(left=left, right=right, scale=0.5)
+        if kind == "channel_delta":
+            return DeltaMixerSpec(heads=int(m["heads"]), kv_heads=int(m.get("kv_heads", m["heads"])), dim=int(m["dim"]),
+                                  vdim=int(m["vdim"]), conv=int(m["conv"]))
+        raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
+
+    def _parse_mlp(self, i: int, mlp: Optional[Dict[str, Any]]) -> Any:
+        if mlp is None:
+            return None
+        kind = mlp.get("kind", "dense")
+        if kind == "dense":
+            return DenseMlpSpec(ff=int(mlp["ff"]), act="gelu_tanh", gated=True)
+        if kind == "moe":
+            r = mlp["router"]
+            shared = mlp.get("shared") or {}
+            return MoeMlpSpec(experts=int(r["experts"]), top=int(r["top"]), ff=int(mlp["expert"]["ff"]), act="glu_clamped",
+                              score="softmax", groups=1, keep=1, scale=1.0, normalise=True, shared_ff=int(shared.get("ff", 0)),
+                              shared_gate=False, gated=True, limit=float(mlp["expert"]["limit"]),
+                              shared_limit=float(shared.get("limit", mlp["expert"]["limit"])), router_bias=True)
+        raise ValueError(f"layer {i}: unknown feed-forward kind {kind!r}")
+
+    def _validate_layer(self, i: int, l: HybridLayerSpec) -> None:
+        m = l.mixer
+        if m.kind == "parallel":
+            a, r = m.left, m.right
+            if min(a.heads, a.kv_heads, a.dim, a.vdim) <= 0 or a.heads % a.kv_heads or a.window < 0:
+                raise ValueError(f"layer {i}: attention sizes heads {a.heads}, kv_heads {a.kv_heads}, window {a.window}")
+            if min(r.heads, r.vdim, r.state, r.groups, r.norm_groups) <= 0 or r.heads % r.groups:
+                raise ValueError(f"layer {i}: {r.heads} state space heads in {r.groups} groups")
+            if (r.heads * r.vdim) % r.norm_groups or not 1 <= r.conv <= 8:
+                raise ValueError(f"layer {i}: inner size {r.heads * r.vdim} in {r.norm_groups} norm groups, {r.conv} taps")
+        else:
+            if min(m.heads, m.kv_heads, m.dim, m.vdim) <= 0 or m.heads % m.kv_heads or not 1 <= m.conv <= 8:
+                raise ValueError(f"layer {i}: delta rule sizes heads {m.heads}, kv_heads {m.kv_heads}, {m.conv} taps")
+        f = l.mlp
+        if f is not None and f.kind == "moe" and not 1 <= f.top <= f.experts:
+            raise ValueError(f"layer {i}: top {f.top} of {f.experts} experts")
+
+    def validate(self) -> None:
+        super().validate()
+        if self.pair_embedding is None or self.pair_embedding.buckets <= 0:
+            raise ValueError("embedding.bigram {buckets, mul_prev, mul_cur} is required")

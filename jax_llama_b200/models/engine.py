@@ -536,7 +536,7 @@ class B200Engine:
             return out
         if self.comm is not None:
             self.comm.begin_sequence()
-        x = self._embed(input_ids.reshape(-1))
+        x = self._embed(input_ids.reshape(-1), cache=cache, B=B, S=S)
         x = self._layers(x, B, S, cache, positions)
         if self.comm is not None:
             self.comm.end_sequence()
@@ -571,8 +571,10 @@ class B200Engine:
         return out
 
     # ------------------------------------------------------------------ model-specific ends of the layer stack
-    def _embed(self, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """Token ids [M] → residual-stream rows [M, H] (the dtype the layer stack of this engine carries)."""
+    def _embed(self, ids: torch.Tensor, out: Optional[torch.Tensor] = None, cache: Optional[DeviceKVCache] = None,
+               B: int = 0, S: int = 0) -> torch.Tensor:
+        """Token ids [M = B·S] → residual-stream rows [M, H] (the dtype the layer stack of this engine carries).  The cache
+        of the request batch comes along for embeddings that depend on a row's earlier tokens."""
         return K.embed(ids, self.embedding, out=out)
 
     def _head(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -719,7 +721,7 @@ class B200Engine:
                 self.comm.end_sequence()
             return
         else:
-            self._embed(st.ids, out=st.x)
+            self._embed(st.ids, out=st.x, cache=cache, B=st.B, S=1)
             x = self._layers(st.x, st.B, 1, cache, None, ws=st)
             if getattr(st, "xn_final", None) is not None:
                 K.linear(st.xn_final, self.lm_head, out_f32=True, out=st.logits)

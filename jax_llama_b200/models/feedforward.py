@@ -16,8 +16,18 @@ from ..ops import seq_kernels as SK
 from .mixers import _stack_rows
 
 
+GLU_ALPHA = 1.702          # slope inside the sigmoid of the clamped gated activation
+
+
+def _gated_act(y: torch.Tensor, u_off: int, F: int, act: str, limit: float, dtype: torch.dtype, **kw) -> torch.Tensor:
+    """The gated activation of a fused gate | up product y fp32 [rows, gate (F) | up at u_off]."""
+    if act == "glu_clamped":
+        return SK.glu_act(y, 0, u_off, F, dtype, kind=SK.GLU_CLAMPED, limit=limit, alpha=GLU_ALPHA, **kw)
+    return SK.glu_act(y, 0, u_off, F, dtype, kind=SK.GLU_PRODUCT, act=SK.ACTIVATIONS[act], **kw)
+
+
 class DenseFeedForward:
-    """down(act(up h))."""
+    """down(act(up h)); gated: down(act(gate h) · (up h)) with gate and up stacked into one product."""
 
     kind = "dense"
 
@@ -25,11 +35,19 @@ class DenseFeedForward:
         if spec.act not in SK.ACTIVATIONS:
             raise ValueError(f"unknown activation {spec.act!r}")
         self.spec, self.act = spec, SK.ACTIVATIONS[spec.act]
-        self.up, self.down = w["up"].contiguous(), w["down"].contiguous()
+        if spec.gated:
+            self.up, offs = _stack_rows([w["gate"], w["up"]])
+            self.u_off = offs[1]
+        else:
+            self.up = w["up"].contiguous()
+        self.down = w["down"].contiguous()
 
     @staticmethod
     def shapes(spec: DenseMlpSpec, W: int) -> Dict[str, Tuple[int, ...]]:
-        return {"up": (spec.ff, W), "down": (W, spec.ff)}
+        out = {"up": (spec.ff, W), "down": (W, spec.ff)}
+        if spec.gated:
+            out["gate"] = (spec.ff, W)
+        return out
 
     def weights(self) -> List[torch.Tensor]:
         return [self.up, self.down]
@@ -38,7 +56,10 @@ class DenseFeedForward:
         return self.weights()
 
     def run(self, h: torch.Tensor) -> torch.Tensor:
-        t = SK.linear(h, self.up, act=self.act, out_f32=False)
+        if self.spec.gated:
+            t = _gated_act(SK.linear(h, self.up), self.u_off, self.spec.ff, self.spec.act, 0.0, h.dtype)
+        else:
+            t = SK.linear(h, self.up, act=self.act, out_f32=False)
         return SK.linear(t, self.down)
 
 
@@ -53,26 +74,43 @@ class MoeFeedForward:
     kind = "moe"
 
     def __init__(self, spec: MoeMlpSpec, w: Dict[str, torch.Tensor]):
-        if spec.act not in SK.ACTIVATIONS or spec.score not in SK.SCORES:
+        if (spec.act not in SK.ACTIVATIONS and not spec.gated) or spec.score not in SK.SCORES:
             raise ValueError(f"unknown activation {spec.act!r} or score function {spec.score!r}")
-        self.spec, self.act, self.score = spec, SK.ACTIVATIONS[spec.act], SK.SCORES[spec.score]
+        if spec.gated and spec.act != "glu_clamped" and spec.act not in SK.ACTIVATIONS:
+            raise ValueError(f"unknown gated activation {spec.act!r}")
+        self.spec, self.act, self.score = spec, SK.ACTIVATIONS.get(spec.act, SK.ACT_NONE), SK.SCORES[spec.score]
         E = spec.experts
-        self.up = torch.stack([w[f"e{e}.up"] for e in range(E)]).contiguous()          # [E, ff, W]
+        self.u_off = self.shared_u_off = 0
+        if spec.gated:                                                                  # [E, gate | up (padded to 8 rows), W]
+            pairs = [_stack_rows([w[f"e{e}.gate"], w[f"e{e}.up"]]) for e in range(E)]
+            self.up, self.u_off = torch.stack([p[0] for p in pairs]).contiguous(), pairs[0][1][1]
+        else:
+            self.up = torch.stack([w[f"e{e}.up"] for e in range(E)]).contiguous()      # [E, ff, W]
         self.down = torch.stack([w[f"e{e}.down"] for e in range(E)]).contiguous()      # [E, W, ff]
+        self.router_bias = w["router.b"].float().contiguous() if spec.router_bias else None
         self.has_shared = spec.shared_ff > 0
         gated = self.has_shared and spec.shared_gate
         self.w_route, offs = _stack_rows([w["router"]] + ([w["shared.sg"]] if gated else []))
         self.gate_off = offs[1] if gated else -1
         self.shared_up = w["shared.up"].contiguous() if self.has_shared else None
+        if self.has_shared and spec.gated:
+            self.shared_up, offs = _stack_rows([w["shared.gate"], w["shared.up"]])
+            self.shared_u_off = offs[1]
         self.shared_down = w["shared.down"].contiguous() if self.has_shared else None
 
     @staticmethod
     def shapes(spec: MoeMlpSpec, W: int) -> Dict[str, Tuple[int, ...]]:
         out: Dict[str, Tuple[int, ...]] = {"router": (spec.experts, W)}
+        if spec.router_bias:
+            out["router.b"] = (spec.experts,)
         for e in range(spec.experts):
             out[f"e{e}.up"], out[f"e{e}.down"] = (spec.ff, W), (W, spec.ff)
+            if spec.gated:
+                out[f"e{e}.gate"] = (spec.ff, W)
         if spec.shared_ff > 0:
             out["shared.up"], out["shared.down"] = (spec.shared_ff, W), (W, spec.shared_ff)
+            if spec.gated:
+                out["shared.gate"] = (spec.shared_ff, W)
             if spec.shared_gate:
                 out["shared.sg"] = (1, W)
         return out
@@ -91,13 +129,20 @@ class MoeFeedForward:
         s = self.spec
         M, W = h.shape
         z = SK.linear(h, self.w_route)                                             # fp32 [M, router logits | gate logit]
-        idx, wt = SK.moe_route(z, s.experts, s.top, s.groups, s.keep, s.group_top, self.score, s.normalise, s.scale)
+        idx, wt = SK.moe_route(z, s.experts, s.top, s.groups, s.keep, s.group_top, self.score, s.normalise, s.scale,
+                               bias=self.router_bias)
+        n_up = self.up.shape[1]                                                    # ff, or gate | up rows of a gated expert
         if M <= SK.MOE_PAIR_ROWS:
             n = M * s.top
             flat = idx.view(-1)
-            t = torch.empty((n, s.ff), dtype=h.dtype, device=h.device)
-            SK.linear_batched(h, self.up, t, nbatch=n, rows=1, x_bs=h.stride(0), o_bs=s.ff, x_div=s.top, w_index=flat,
-                              act=self.act)
+            if s.gated:
+                gu = torch.empty((n, n_up), dtype=torch.float32, device=h.device)
+                SK.linear_batched(h, self.up, gu, nbatch=n, rows=1, x_bs=h.stride(0), o_bs=n_up, x_div=s.top, w_index=flat)
+                t = _gated_act(gu, self.u_off, s.ff, s.act, s.limit, h.dtype)
+            else:
+                t = torch.empty((n, s.ff), dtype=h.dtype, device=h.device)
+                SK.linear_batched(h, self.up, t, nbatch=n, rows=1, x_bs=h.stride(0), o_bs=s.ff, x_div=s.top, w_index=flat,
+                                  act=self.act)
             y = torch.empty((n, W), dtype=torch.float32, device=h.device)
             SK.linear_batched(t, self.down, y, nbatch=n, rows=1, x_bs=s.ff, o_bs=W, w_index=flat)
             pos = None
@@ -105,19 +150,32 @@ class MoeFeedForward:
             # sorted rows in 128-row segments, gathered once, then the grouped tcgen05 GEMM twice
             pos, row_src, tile_group, used = SK.moe_sort(idx, s.experts, tile=SK.GEMM_TILE_ROWS)
             xs = SK.moe_gather(h, row_src)
-            t = SK.gemm_grouped(xs, self.up, tile_group, act=self.act, out_f32=False, tiles_used=used)
+            if s.gated:
+                gu = SK.gemm_grouped(xs, self.up, tile_group, tiles_used=used)
+                t = _gated_act(gu, self.u_off, s.ff, s.act, s.limit, h.dtype, rows_used=used, rows_mult=SK.GEMM_TILE_ROWS,
+                               zero=True)
+            else:
+                t = SK.gemm_grouped(xs, self.up, tile_group, act=self.act, out_f32=False, tiles_used=used)
             y = SK.gemm_grouped(t, self.down, tile_group, tiles_used=used)
         else:
             pos, row_src, tile_group, _ = SK.moe_sort(idx, s.experts)
             rows = row_src.shape[0]
-            t = torch.empty((rows, s.ff), dtype=h.dtype, device=h.device)
-            SK.linear_sorted(h, self.up, t, tile_group, row_src, act=self.act)
+            if s.gated:
+                gu = torch.empty((rows, n_up), dtype=torch.float32, device=h.device)
+                SK.linear_sorted(h, self.up, gu, tile_group, row_src)
+                t = _gated_act(gu, self.u_off, s.ff, s.act, s.limit, h.dtype)
+            else:
+                t = torch.empty((rows, s.ff), dtype=h.dtype, device=h.device)
+                SK.linear_sorted(h, self.up, t, tile_group, row_src, act=self.act)
             y = torch.empty((rows, W), dtype=torch.float32, device=h.device)
             SK.linear_sorted(t, self.down, y, tile_group, None)
         shared: Optional[torch.Tensor] = None
         gate = None
         if self.has_shared:
-            u = SK.linear(h, self.shared_up, act=self.act, out_f32=False)
+            if s.gated:
+                u = _gated_act(SK.linear(h, self.shared_up), self.shared_u_off, s.shared_ff, s.act, s.shared_limit, h.dtype)
+            else:
+                u = SK.linear(h, self.shared_up, act=self.act, out_f32=False)
             shared = SK.linear(u, self.shared_down)
             if self.gate_off >= 0:
                 gate = z[:, self.gate_off:self.gate_off + 1]

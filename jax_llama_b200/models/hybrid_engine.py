@@ -37,10 +37,11 @@ class HybridCache(DeviceKVCache):
     """Per-layer caches of unequal shapes plus recurrent states.  `k` / `v` of the base class point at the first
     attention layer's tensors (identity of the cache for graph keys)."""
 
-    ks: List[Optional[torch.Tensor]] = field(default_factory=list)
-    vs: List[Optional[torch.Tensor]] = field(default_factory=list)
-    states: List[Optional[torch.Tensor]] = field(default_factory=list)
+    ks: List[Any] = field(default_factory=list)          # per layer: a tensor, None, or a tuple (a layer of several mixers)
+    vs: List[Any] = field(default_factory=list)
+    states: List[Any] = field(default_factory=list)      # per layer: fp32 tensor(s) carried from token to token
     length: int = 0
+    prev_tok: Optional[torch.Tensor] = None              # int32 [B]: every row's last token (embeddings that hash token pairs)
 
     @property
     def capacity(self) -> int:
@@ -49,12 +50,20 @@ class HybridCache(DeviceKVCache):
     def set_index(self, value: int) -> None:
         super().set_index(value)
         if int(value) == 0:                       # a new request batch starts from an empty state
-            for s in self.states:
-                if s is not None:
-                    s.zero_()
+            for s in _tensors(self.states):
+                s.zero_()
 
     def mutable_state(self) -> List[torch.Tensor]:
-        return [self.len_dev] + [s for s in self.states if s is not None]
+        return [self.len_dev] + _tensors(self.states) + ([self.prev_tok] if self.prev_tok is not None else [])
+
+
+def _tensors(obj: Any) -> List[torch.Tensor]:
+    """The tensors of a nest of lists / tuples (None entries skipped)."""
+    if obj is None:
+        return []
+    if isinstance(obj, torch.Tensor):
+        return [obj]
+    return [t for o in obj for t in _tensors(o)]
 
 
 @dataclass
@@ -67,18 +76,33 @@ class HybridLayer:
     ff: Any = None
 
 
-def tensor_shapes(config: Any, decay_rank: int = 16) -> Dict[str, Tuple[int, ...]]:
+def tensor_shapes(config: Any, decay_rank: int = 16, present: Optional[Dict[str, Tuple[int, ...]]] = None
+                  ) -> Dict[str, Tuple[int, ...]]:
     """Checkpoint tensor names → shapes for a config of this family (what a loader expects, what random_init draws).
-    The rank of the decay projection is not a config key: a checkpoint fixes it by the shape of ``mix.a1``."""
+    The ranks of low-rank projections are not config keys: a checkpoint fixes them by the shapes of its tensors
+    (`present`: name → shape of what the checkpoint holds; absent: `decay_rank`)."""
     W = config.hidden_size
     sandwich = config.block == "sandwich"
-    out: Dict[str, Tuple[int, ...]] = {"embed": (config.vocab_size, W), "final.norm": (W,), "head": (config.vocab_size, W)}
+    out: Dict[str, Tuple[int, ...]] = {"embed": (config.vocab_size, W), "final.norm": (W,)}
+    if not config.tied_head:
+        out["head"] = (config.vocab_size, W)
+    if config.embed_norm:
+        out["embed.norm"] = (W,)
+    if config.pair_embedding is not None:
+        out["bigram"] = (config.pair_embedding.buckets + 1, W)
     for i, l in enumerate(config.layers):
         p, m = f"l{i}.", l.mixer
         out[p + "norm1"] = (W,)
         if sandwich:
             out[p + "norm1b"] = (W,)
-        if m.kind == "gla":
+        if hasattr(MIXERS[m.kind], "shapes"):
+
+            def rank_of(name: str, default: int, prefix: str = p + "mix.") -> int:
+                return int(present[prefix + name][0]) if present and prefix + name in present else int(decay_rank)
+
+            for name, shape in MIXERS[m.kind].shapes(m, W, rank_of).items():
+                out[p + "mix." + name] = shape
+        elif m.kind == "gla":
             out.update({p + "mix.q": (m.heads * m.dim, W), p + "mix.k": (m.heads * m.dim, W),
                         p + "mix.v": (m.heads * m.vdim, W), p + "mix.g": (m.heads * m.vdim, W),
                         p + "mix.o": (W, m.heads * m.vdim), p + "mix.norm": (m.vdim,), p + "mix.a1": (decay_rank, W),
@@ -101,7 +125,8 @@ def tensor_shapes(config: Any, decay_rank: int = 16) -> Dict[str, Tuple[int, ...
                 out[p + "mix.g"] = (m.heads, W)
             out[p + "mix.o"] = (W, m.heads * m.vdim)
         if l.mlp is not None:
-            out[p + "norm2"] = (W,)
+            if config.block != "parallel_shared":
+                out[p + "norm2"] = (W,)
             if sandwich:
                 out[p + "norm2b"] = (W,)
             for name, shape in FEED_FORWARDS[l.mlp.kind].shapes(l.mlp, W).items():
@@ -130,17 +155,15 @@ class HybridEngine(B200Engine):
         self.mega_max_batch = 0
         self.eps = float(config.rms_norm_eps)
         self.norm_offset = float(config.norm_offset)          # 1: norm weights are stored around zero
-        if config.block not in ("sandwich", "parallel"):
+        if config.block not in ("sandwich", "parallel", "parallel_shared"):
             raise ValueError(f"unknown block form {config.block!r}")
-        self.parallel = config.block == "parallel"
+        self.parallel = config.block in ("parallel", "parallel_shared")
+        self.shared_norm = config.block == "parallel_shared"      # one norm per block, read by both sublayers
         if self.parallel and self.norm_offset != 0.0:
             raise ValueError("parallel blocks take plain norm weights")
-        want = None
-        for name, t in tensors.items():
-            if name.endswith("mix.a1"):
-                want = tensor_shapes(config, decay_rank=int(t.shape[0]))
-                break
-        want = want or tensor_shapes(config)
+        present = {name: tuple(t.shape) for name, t in tensors.items()}
+        rank = next((int(t.shape[0]) for name, t in tensors.items() if name.endswith("mix.a1")), 16)
+        want = tensor_shapes(config, decay_rank=rank, present=present)
         missing = sorted(set(want) - set(tensors))
         if missing:
             raise ValueError(f"checkpoint lacks tensors: {missing[:8]}{' ...' if len(missing) > 8 else ''}")
@@ -153,7 +176,9 @@ class HybridEngine(B200Engine):
 
         self.embedding = get("embed")
         self.final_norm = get("final.norm")
-        self.lm_head = get("head")
+        self.lm_head = self.embedding if config.tied_head else get("head")
+        self.embed_norm = get("embed.norm") if config.embed_norm else None
+        self.pair_table = get("bigram") if config.pair_embedding is not None else None
         self.v_local = config.vocab_size
         self.layers: List[HybridLayer] = []
         for i, l in enumerate(config.layers):
@@ -163,7 +188,8 @@ class HybridEngine(B200Engine):
             if not self.parallel:
                 layer.norm1b = get(p + "norm1b")
             if l.mlp is not None:
-                layer.norm2 = get(p + "norm2")
+                if not self.shared_norm:
+                    layer.norm2 = get(p + "norm2")
                 if not self.parallel:
                     layer.norm2b = get(p + "norm2b")
                 fw = {k[len(p) + 4:]: get(k) for k in want if k.startswith(p + "mlp.")}
@@ -192,7 +218,7 @@ class HybridEngine(B200Engine):
 
     def weight_bytes_per_step(self, rows: int = 1) -> int:
         """Bytes of weights a decode step of `rows` tokens streams (a mixture of experts: the experts it can touch)."""
-        ws = [self.lm_head, self.final_norm]
+        ws = [self.lm_head, self.final_norm] + [t for t in (self.embed_norm,) if t is not None]
         for l in self.layers:
             ws += l.mixer.weights() + [t for t in (l.norm1, l.norm1b, l.norm2, l.norm2b) if t is not None]
             if l.ff is not None:
@@ -231,17 +257,28 @@ class HybridEngine(B200Engine):
             ks.append(kv[0] if kv is not None else None)
             vs.append(kv[1] if kv is not None else None)
             states.append(l.mixer.new_state(batch, self.device))
-        first = next((k for k in ks if k is not None), None)
+        first = next(iter(_tensors(ks)), None)
         ident = first if first is not None else torch.zeros(1, dtype=self.dtype, device=self.device)
         self._check_max_length(max_length)
+        prev = torch.zeros(batch, dtype=torch.int32, device=self.device) if self.pair_table is not None else None
         return HybridCache(k=ident, v=ident, index=0,
                            pad_left=torch.zeros(batch, dtype=torch.int32, device=self.device),
                            len_dev=torch.zeros(1, dtype=torch.int32, device=self.device),
-                           ks=ks, vs=vs, states=states, length=int(max_length))
+                           ks=ks, vs=vs, states=states, length=int(max_length), prev_tok=prev)
 
     # ------------------------------------------------------------------ layer stack
-    def _embed(self, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        return SK.embed_f32(ids, self.embedding, out=out)
+    def _embed(self, ids: torch.Tensor, out: Optional[torch.Tensor] = None, cache: Optional[HybridCache] = None,
+               B: int = 0, S: int = 0) -> torch.Tensor:
+        if self.pair_table is not None:
+            pe = self.config.pair_embedding
+            if cache is None or cache.prev_tok is None:
+                raise ValueError("an embedding that hashes token pairs needs the cache of the request batch")
+            return SK.embed_pair_norm(ids, self.embedding, self.pair_table, self.embed_norm, cache.prev_tok, cache.len_dev,
+                                      cache.pad_left, B, S, pe.buckets, pe.mul_prev, pe.mul_cur, self.eps, out=out)
+        x = SK.embed_f32(ids, self.embedding, out=out)
+        if self.embed_norm is not None:
+            raise NotImplementedError("a norm after a plain embedding")
+        return x
 
     def _head(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         c = self.config
@@ -263,8 +300,7 @@ class HybridEngine(B200Engine):
         h = SK.norm_f32(x, self.layers[0].norm1, eps, off)
         for i, l in enumerate(self.layers):
             rope = self._rope_for(getattr(l.mixer.spec, "rot", None), cache.capacity)
-            u = l.mixer.run(h, B, S, cache, i, rope)
-            z = SK.linear(u, l.mixer.wo)
+            z = l.mixer.forward(h, B, S, cache, i, rope)
             nxt = l.norm2 if l.ff is not None else (self.layers[i + 1].norm1 if i + 1 < n else None)
             h = SK.postnorm_add(z, l.norm1b, x, eps, off, w_next=nxt)
             if l.ff is not None:
@@ -290,6 +326,8 @@ class HybridEngine(B200Engine):
         first = self.layers[0]
         h1, h2 = SK.branch_add_norm(x, None, None, mult, first.norm1, first.norm2 if first.ff is not None else None, eps)
         for i, l in enumerate(self.layers):
+            if self.shared_norm:
+                h2 = h1
             rope = self._rope_for(getattr(l.mixer.spec, "rot", None), cache.capacity)
             y2 = None
             forked = overlap and l.ff is not None
@@ -300,8 +338,7 @@ class HybridEngine(B200Engine):
                 with torch.cuda.stream(side):
                     y2 = l.ff.run(h2)
                     join.record(side)
-            u = l.mixer.run(h1, B, S, cache, i, rope)
-            y1 = SK.linear(u, l.mixer.wo)
+            y1 = l.mixer.forward(h1, B, S, cache, i, rope)
             if forked:
                 main.wait_event(join)
             elif l.ff is not None:

@@ -16,7 +16,8 @@ from typing import Dict, List, Optional, Tuple
 
 import torch
 
-from ..config import AttentionMixerSpec, GlaMixerSpec, LatentAttentionMixerSpec, RetentionMixerSpec, RotaryScaling
+from ..config import (AttentionMixerSpec, DeltaMixerSpec, GlaMixerSpec, LatentAttentionMixerSpec, ParallelMixerSpec,
+                      RetentionMixerSpec, RotaryScaling, StateSpaceMixerSpec)
 from ..ops import _lib
 from ..ops import kernels as K
 from ..ops import seq_kernels as SK
@@ -63,10 +64,41 @@ def rotary_table(dims: int, base: float, length: int, device: torch.device, scal
             (torch.sin(ang) * mult).float().to(device).contiguous())
 
 
-class AttentionMixer:
+class Mixer:
+    """What the layer stack asks of a mixer.  `run` gives the input of the output projection `wo`; `forward` the mixer's
+    fp32 contribution [M, width] (a mixer made of several overrides it).  `shapes(spec, W, rank_of)` lists the checkpoint
+    tensors under the mixer's prefix; `rank_of(name, default)` is the first dimension the checkpoint gives a tensor whose
+    inner size no configuration key fixes."""
+
+    def forward(self, h: torch.Tensor, B: int, S: int, cache: "object", layer: int, rope: Optional[Tuple] = None
+                ) -> torch.Tensor:
+        return SK.linear(self.run(h, B, S, cache, layer, rope), self.wo)
+
+
+class _CacheView:
+    """The cache as one of several mixers of a layer sees it: the shared fill level and left-pad counts, and that mixer's
+    own entries under the layer's index."""
+
+    def __init__(self, cache: "object", layer: int, side: int):
+        self._cache = cache
+        self.ks = {layer: cache.ks[layer][side] if cache.ks[layer] is not None else None}
+        self.vs = {layer: cache.vs[layer][side] if cache.vs[layer] is not None else None}
+        self.states = {layer: cache.states[layer][side] if cache.states[layer] is not None else None}
+
+    def __getattr__(self, name: str) -> "object":
+        return getattr(self._cache, name)
+
+
+class AttentionMixer(Mixer):
     """Softmax attention: grouped key / value heads, query / key size `dim` and value size `vdim` (they may differ),
     rotary embedding on the first `rot.dims` channels, optional unit-RMS q / k, optional sigmoid gate per head,
-    optional reuse of another layer's cache (`kv_from`)."""
+    optional reuse of another layer's cache (`kv_from`); optional q / k / v biases, unit-RMS values, sliding window, a
+    sink in the softmax denominator and mixing of the heads' weights by a [heads, heads] matrix.
+
+    With mixed weights head h's output is Σ_j (Σ_g T[h, g] p_g(j)) v_c(j) = Σ_g T[h, g] (Σ_j p_g(j) v_c(j)), c its own
+    key/value head: the attention kernel forms, per query head g, the weighted sums over the values of ALL key/value heads
+    (the value cache is token-major, one row [kv_heads · vdim] per token, read as one wide value head) in fp32, and a
+    second small kernel mixes them.  The sink's share is not mixed: it has no values."""
 
     kind = "attention"
 
@@ -81,14 +113,42 @@ class AttentionMixer:
         self.wo = w["o"].contiguous()
         self.dtype = self.wo.dtype
         self._decode_plans: Dict[Tuple[int, int], Tuple[int, Optional[torch.Tensor]]] = {}
+        self.bias: Optional[torch.Tensor] = None
+        if spec.bias:                                      # fp32 over the columns of the stacked projection
+            self.bias = torch.zeros(self.w_in.shape[0], dtype=torch.float32, device=self.wo.device)
+            for name, off in (("q", self.q_off), ("k", self.k_off), ("v", self.v_off)):
+                if off >= 0:
+                    self.bias[off:off + w[name].shape[0]] = w[name + ".b"].float()
+        self.talk = w["talk"].contiguous() if spec.talking_heads else None
+        if spec.talking_heads and (self.shares_kv or spec.head_gate):
+            raise ValueError("mixed attention weights go with a layer's own keys / values and no head gate")
+        self.plain = not (spec.bias or spec.v_unit_norm or spec.window or spec.sink or spec.talking_heads)
+
+    @staticmethod
+    def shapes(spec: AttentionMixerSpec, W: int, rank_of: "object" = None) -> Dict[str, Tuple[int, ...]]:
+        out: Dict[str, Tuple[int, ...]] = {"q": (spec.heads * spec.dim, W), "o": (W, spec.heads * spec.vdim)}
+        if spec.kv_from is None:
+            out["k"], out["v"] = (spec.kv_heads * spec.dim, W), (spec.kv_heads * spec.vdim, W)
+        if spec.head_gate:
+            out["g"] = (spec.heads, W)
+        if spec.bias:
+            for n in ("q", "k", "v"):
+                if n in out:
+                    out[n + ".b"] = (out[n][0],)
+        if spec.talking_heads:
+            out["talk"] = (spec.heads, spec.heads)
+        return out
 
     def weights(self) -> List[torch.Tensor]:
-        return [self.w_in, self.wo]
+        return [self.w_in, self.wo] + ([self.talk] if self.talk is not None else [])
 
     def new_cache(self, batch: int, length: int, device: torch.device) -> Optional[Tuple[torch.Tensor, torch.Tensor]]:
         if self.shares_kv:
             return None
         s = self.spec
+        if s.talking_heads:                                # values token-major: every query head reads all value heads
+            return (torch.zeros((batch, s.kv_heads, length, s.dim), dtype=self.dtype, device=device),
+                    torch.zeros((batch, length, s.kv_heads * s.vdim), dtype=self.dtype, device=device))
         return (torch.zeros((batch, s.kv_heads, length, s.dim), dtype=self.dtype, device=device),
                 torch.zeros((batch, s.kv_heads, length, s.vdim), dtype=self.dtype, device=device))
 
@@ -105,8 +165,17 @@ class AttentionMixer:
         rot = s.rot.dims if s.rot is not None else 0
         SK.attn_prep(y, self.q_off, self.k_off, self.v_off, q, None if self.shares_kv else kc,
                      None if self.shares_kv else vc, rope[0], rope[1], rot, s.qk_unit_norm, self.eps, cache.len_dev,
-                     cache.pad_left, B, S, s.heads, s.kv_heads, s.dim, s.vdim)
+                     cache.pad_left, B, S, s.heads, s.kv_heads, s.dim, s.vdim, bias=self.bias, v_unit_norm=s.v_unit_norm,
+                     v_token_major=s.talking_heads)
+        if s.talking_heads:
+            return self._attend_mixed(q, kc, vc, cache, B, S)
         gate = y[:, self.g_off:self.g_off + s.heads] if s.head_gate else None
+        if not self.plain:
+            if gate is not None:
+                raise NotImplementedError("a head gate with a window or a sink")
+            T = kc.shape[2]
+            return SK.attn_windowed(q, kc, vc, cache.len_dev, cache.pad_left, B, S, s.heads, s.kv_heads, s.dim, s.vdim, T,
+                                    s.dim, s.vdim, s.window, s.scale, sink=s.sink)
         if self._library_shape():
             # 64- / 128-wide heads in bfloat16 are the shapes the LLaMA kernels are built for: the tcgen05 flash kernel
             # for prompts, the split-KV kernel for one new token; both take the score scale as an argument
@@ -115,6 +184,25 @@ class AttentionMixer:
                 SK.head_gate(out, gate, s.heads, s.vdim)
             return out
         return SK.attn_generic(q, kc, vc, gate, cache.len_dev, cache.pad_left, B, S, s.heads, s.scale)
+
+    MAX_VALUE_ROW = 512            # widest value row the attention kernels take in one call
+
+    def _attend_mixed(self, q: torch.Tensor, kc: torch.Tensor, vc: torch.Tensor, cache: "object", B: int, S: int
+                      ) -> torch.Tensor:
+        """Weighted sums of every query head over all value heads (fp32), then the mix across heads.  Value heads are
+        taken `MAX_VALUE_ROW // vdim` at a time."""
+        s = self.spec
+        M, H, G, T = B * S, s.heads, s.kv_heads, kc.shape[2]
+        out = torch.empty((M, H * s.vdim), dtype=self.dtype, device=q.device)
+        per = max(1, min(G, self.MAX_VALUE_ROW // s.vdim))
+        row = G * s.vdim
+        for c0 in range(0, G, per):
+            gc = min(per, G - c0)
+            v = vc[:, :, c0 * s.vdim:]                                # same row pitch, first column of this group of heads
+            o = SK.attn_windowed(q, kc, v, cache.len_dev, cache.pad_left, B, S, H, G, s.dim, gc * s.vdim, T, s.dim, row,
+                                 s.window, s.scale, strides=(G * T * s.dim, T * s.dim, T * row, 0), sink=s.sink, out_f32=True)
+            SK.talk_mix(o, self.talk, out, H, G, gc, c0, s.vdim)
+        return out
 
     def _library_shape(self) -> bool:
         s = self.spec
@@ -142,7 +230,7 @@ class AttentionMixer:
         return out
 
 
-class GlaMixer:
+class GlaMixer(Mixer):
     """Gated linear attention: S_t = diag(alpha_t) S_(t-1) + k_t v_tᵀ, o_t = S_tᵀ q_t per head, alpha from a low-rank
     projection through sigmoid(·)^(1/tau); read-out normalised per head (plain weight shared by the heads), gated by
     silu of a projection of the input.  The state is fp32 and is what the layer keeps between tokens."""
@@ -179,7 +267,7 @@ class GlaMixer:
         return SK.headnorm_gate(o, self.norm, gate, s.heads, s.vdim, self.eps, SK.ACT_SILU)
 
 
-class LatentAttentionMixer:
+class LatentAttentionMixer(Mixer):
     """Softmax attention through low-rank latents.  Per token the layer keeps one row [normed key/value latent | rotated
     key part shared by the heads]; nothing per head.
 
@@ -269,7 +357,7 @@ class LatentAttentionMixer:
                                 s.scale, strides=(S * H * qd, qd, S * ldv, s.vdim))
 
 
-class RetentionMixer:
+class RetentionMixer(Mixer):
     """Retention: linear attention with one fixed decay per head, S_t = decay_h S_(t-1) + k_t v_tᵀ, o_t = S_tᵀ q_t, rotary
     q / k, k scaled by dim^(-1/2) after the rotation; every head's read-out divided by its RMS (no weight) and gated by
     silu of a projection of the input.  The fp32 state is what the layer keeps between tokens."""
@@ -307,6 +395,160 @@ class RetentionMixer:
         return SK.headnorm_gate(o, None, gate, s.heads, s.vdim, self.eps, SK.ACT_SILU, dtype=self.dtype)
 
 
+class StateSpaceMixer(Mixer):
+    """Selective state space layer.  One stacked projection [z | x | B | C | dt]; x, B, C through a causal convolution
+    (state: its last taps − 1 inputs) and silu; dt = softplus(dt + bias); per head S_t = exp(−exp(A_log) dt) S_(t−1) +
+    dt B_t x_tᵀ, y_t = S_tᵀ C_t + D x_t — the scan kernels of gated linear attention with keys B, queries C (shared by the
+    heads of a group), values dt · x and one decay per (token, head); then y · silu(z), an RMS norm over each of
+    `norm_groups` parts of the row, the weight, and the output projection.  Step size, decay, state and norm are fp32."""
+
+    kind = "state_space"
+
+    def __init__(self, spec: StateSpaceMixerSpec, w: Dict[str, torch.Tensor], eps: float):
+        self.spec, self.eps = spec, float(eps)
+        s = spec
+        self.inner = s.heads * s.vdim
+        self.gn = s.groups * s.state
+        self.w_in, _ = _stack_rows([w["in"]])
+        self.z_off, self.x_off = 0, self.inner
+        self.dt_off = 2 * self.inner + 2 * self.gn
+        self.conv_w, self.conv_b = w["conv"].contiguous(), w["conv.b"].contiguous()
+        self.dt_bias, self.a_log, self.skip = w["dt_bias"].contiguous(), w["A_log"].contiguous(), w["D"].contiguous()
+        self.norm = w["norm"].contiguous()
+        self.wo = w["o"].contiguous()
+        self.dtype = self.wo.dtype
+
+    @staticmethod
+    def shapes(spec: StateSpaceMixerSpec, W: int, rank_of: "object" = None) -> Dict[str, Tuple[int, ...]]:
+        inner, gn = spec.heads * spec.vdim, spec.groups * spec.state
+        return {"in": (2 * inner + 2 * gn + spec.heads, W), "conv": (inner + 2 * gn, spec.conv), "conv.b": (inner + 2 * gn,),
+                "dt_bias": (spec.heads,), "A_log": (spec.heads,), "D": (spec.heads,), "norm": (inner,), "o": (W, inner)}
+
+    def weights(self) -> List[torch.Tensor]:
+        return [self.w_in, self.conv_w, self.conv_b, self.dt_bias, self.a_log, self.skip, self.norm, self.wo]
+
+    def new_cache(self, batch: int, length: int, device: torch.device) -> None:
+        return None
+
+    def new_state(self, batch: int, device: torch.device) -> Tuple[torch.Tensor, torch.Tensor]:
+        s = self.spec
+        return (torch.zeros((batch, s.heads, s.state, s.vdim), dtype=torch.float32, device=device),
+                torch.zeros((batch, max(s.conv - 1, 1), self.inner + 2 * self.gn), dtype=torch.float32, device=device))
+
+    def run(self, h: torch.Tensor, B: int, S: int, cache: "object", layer: int, rope: Optional[Tuple] = None
+            ) -> torch.Tensor:
+        s = self.spec
+        state, conv_state = cache.states[layer]
+        y = SK.linear(h, self.w_in)                                   # fp32 [M, z | x | B | C | dt]
+        u = SK.causal_conv(y, self.x_off, self.conv_w, self.conv_b, conv_state, cache.len_dev, cache.pad_left, B, S,
+                           act=SK.ACT_SILU)                           # fp32 [M, x | B | C]
+        o = SK.ssd_scan(y, self.dt_off, self.dt_bias, self.a_log, u, self.inner + self.gn, self.inner, 0, s.groups, state,
+                        cache.len_dev, cache.pad_left, B, S, s.heads, s.state, s.vdim)
+        return SK.gated_groupnorm(o, u[:, :self.inner], self.skip, s.vdim, y[:, self.z_off:self.z_off + self.inner], self.norm,
+                                  s.norm_groups, self.eps, SK.ACT_SILU)
+
+
+class DeltaRuleMixer(Mixer):
+    """Gated delta rule with one decay per key channel (see `DeltaMixerSpec`).  One stacked projection
+    [q | k | v | beta | decay rank | gate rank]; q, k, v through ONE causal convolution call (their filters stacked; state:
+    the last taps − 1 inputs) and silu; the scan kernels normalise q / k, form beta and the decays
+    exp(−exp(A_log) softplus(A2 · + bias)) and advance the fp32 state; the read-out is normed per head (weight shared by
+    the heads) and gated by sigmoid of the low-rank gate."""
+
+    kind = "channel_delta"
+
+    def __init__(self, spec: DeltaMixerSpec, w: Dict[str, torch.Tensor], eps: float):
+        self.spec, self.eps = spec, float(eps)
+        s = spec
+        self.w_in, offs = _stack_rows([w["q"], w["k"], w["v"], w["b"], w["a1"], w["g1"]])
+        self.q_off, self.k_off, self.v_off, self.b_off, self.a_off, self.g_off = offs
+        self.nq, self.nv = s.kv_heads * s.dim, s.heads * s.vdim
+        self.conv_w = torch.cat([w["q.conv"], w["k.conv"], w["v.conv"]], 0).contiguous()
+        self.a2, self.a_bias, self.a_log = w["a2"].contiguous(), w["dt_bias"].contiguous(), w["A_log"].contiguous()
+        self.g2 = w["g2"].contiguous()
+        self.gate_rank = w["g1"].shape[0]
+        self.norm = w["norm"].contiguous()
+        self.wo = w["o"].contiguous()
+        self.dtype = self.wo.dtype
+
+    @staticmethod
+    def shapes(spec: DeltaMixerSpec, W: int, rank_of: "object" = None) -> Dict[str, Tuple[int, ...]]:
+        rank_of = rank_of or (lambda name, default: default)
+        nq, nv, nd = spec.kv_heads * spec.dim, spec.heads * spec.vdim, spec.heads * spec.dim
+        ra, rg = rank_of("a1", 16), rank_of("g1", 16)
+        return {"q": (nq, W), "q.conv": (nq, spec.conv), "k": (nq, W), "k.conv": (nq, spec.conv), "v": (nv, W),
+                "v.conv": (nv, spec.conv), "b": (spec.heads, W), "A_log": (spec.heads,), "norm": (spec.vdim,), "a1": (ra, W),
+                "a2": (nd, ra), "dt_bias": (nd,), "g1": (rg, W), "g2": (nv, rg), "o": (W, nv)}
+
+    def weights(self) -> List[torch.Tensor]:
+        return [self.w_in, self.conv_w, self.a2, self.a_bias, self.a_log, self.g2, self.norm, self.wo]
+
+    def new_cache(self, batch: int, length: int, device: torch.device) -> None:
+        return None
+
+    def new_state(self, batch: int, device: torch.device) -> Tuple[torch.Tensor, torch.Tensor]:
+        s = self.spec
+        return (torch.zeros((batch, s.heads, s.dim, s.vdim), dtype=torch.float32, device=device),
+                torch.zeros((batch, max(s.conv - 1, 1), 2 * self.nq + self.nv), dtype=torch.float32, device=device))
+
+    def run(self, h: torch.Tensor, B: int, S: int, cache: "object", layer: int, rope: Optional[Tuple] = None
+            ) -> torch.Tensor:
+        s = self.spec
+        state, conv_state = cache.states[layer]
+        y = SK.linear(h, self.w_in)                                   # fp32 [M, q | k | v | beta | decay rank | gate rank]
+        u = SK.causal_conv(y, self.q_off, self.conv_w, None, conv_state, cache.len_dev, cache.pad_left, B, S, act=SK.ACT_SILU)
+        o = SK.delta_scan(u, 0, self.nq, 2 * self.nq, s.kv_heads, y, self.b_off, self.a_off, self.a2, self.a_bias,
+                          self.a_log, state, cache.len_dev, cache.pad_left, B, S, s.heads, s.dim, s.vdim)
+        g_in = SK.act_cast(y[:, self.g_off:self.g_off + self.gate_rank], self.dtype)
+        gate = SK.linear(g_in, self.g2)                               # fp32 [M, heads · vdim]
+        return SK.headnorm_gate(o, self.norm, gate, s.heads, s.vdim, self.eps, SK.ACT_SIGMOID)
+
+
+class ParallelMixer(Mixer):
+    """Two mixers side by side on the same input: scale · (norm(left(h)) · w_left + norm(right(h)) · w_right), the norms
+    over the model width.  Each side keeps its own cache / state; the layer's cache entries are pairs."""
+
+    kind = "parallel"
+
+    def __init__(self, spec: ParallelMixerSpec, w: Dict[str, torch.Tensor], eps: float):
+        self.spec, self.eps = spec, float(eps)
+        self.sides = []
+        for side, sub in (("left", spec.left), ("right", spec.right)):
+            sw = {k[len(side) + 1:]: v for k, v in w.items() if k.startswith(side + ".") and k != side + ".out"}
+            self.sides.append(MIXERS[sub.kind](sub, sw, eps))
+        self.out_norms = [w["left.out"].contiguous(), w["right.out"].contiguous()]
+        self.dtype = self.out_norms[0].dtype
+
+    @staticmethod
+    def shapes(spec: ParallelMixerSpec, W: int, rank_of: "object" = None) -> Dict[str, Tuple[int, ...]]:
+        out: Dict[str, Tuple[int, ...]] = {}
+        for side, sub in (("left", spec.left), ("right", spec.right)):
+            sub_rank = (lambda name, default, side=side: rank_of(side + "." + name, default)) if rank_of else None
+            for name, shape in MIXERS[sub.kind].shapes(sub, W, sub_rank).items():
+                out[f"{side}.{name}"] = shape
+            out[f"{side}.out"] = (W,)
+        return out
+
+    def weights(self) -> List[torch.Tensor]:
+        return [t for m in self.sides for t in m.weights()] + self.out_norms
+
+    def new_cache(self, batch: int, length: int, device: torch.device) -> Optional[Tuple]:
+        got = [m.new_cache(batch, length, device) for m in self.sides]
+        if all(g is None for g in got):
+            return None
+        return (tuple(g[0] if g is not None else None for g in got), tuple(g[1] if g is not None else None for g in got))
+
+    def new_state(self, batch: int, device: torch.device) -> Optional[Tuple]:
+        got = [m.new_state(batch, device) for m in self.sides]
+        return None if all(g is None for g in got) else tuple(got)
+
+    def forward(self, h: torch.Tensor, B: int, S: int, cache: "object", layer: int, rope: Optional[Tuple] = None
+                ) -> torch.Tensor:
+        ys = [m.forward(h, B, S, _CacheView(cache, layer, i), layer, rope) for i, m in enumerate(self.sides)]
+        return SK.norm_mean2(ys[0], self.out_norms[0], ys[1], self.out_norms[1], self.spec.scale, self.eps)
+
+
 MIXERS = {"attention": AttentionMixer, "gla": GlaMixer, "latent_attention": LatentAttentionMixer,
-          "retention": RetentionMixer}
+          "retention": RetentionMixer, "state_space": StateSpaceMixer, "channel_delta": DeltaRuleMixer,
+          "parallel": ParallelMixer}
 

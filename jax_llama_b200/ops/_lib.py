@@ -53,7 +53,7 @@ _SIGNATURES = {
     "jl_decode_advance": (i32, [ip, ip, ip, ip, i32, i32, i32, i32, ip, ip, ip, ip, vp]),
 }
 
-# kernels of the hybrid decoder family (csrc/seq_*.cu, attn_generic.cu, gla_scan.cu)
+# kernels of the hybrid decoder family (csrc/seq_*.cu, attn_generic.cu, gla_scan.cu, delta_scan.cu, moe.cu)
 _HYBRID = {
     "jl_embed_f32": (i32, [ip, vp, fp, i32, i32, i32, i32, vp]),
     "jl_norm_f32": (i32, [fp, vp, vp, i32, i32, f32, f32, i32, vp]),
@@ -62,7 +62,7 @@ _HYBRID = {
     "jl_act_cast": (i32, [fp, i32, vp, i32, i32, i32, i32, f32, f32, i32, vp]),
     "jl_act_inplace": (i32, [vp, i32, i32, i32, i32, f32, f32, i32, vp]),
     "jl_linear_any": (i32, [vp, i32, vp, vp, i32, i32, i32, i32, i32, f32, f32, i32, i32, vp]),
-    "jl_attn_prep": (i32, [fp, i32, i32, i32, i32, vp, vp, vp, fp, fp, i32, i32, i32, f32, ip, ip] + [i32] * 8 + [vp]),
+    "jl_attn_prep": (i32, [fp, i32, i32, i32, i32, vp, vp, vp, fp, fp, i32, i32, i32, f32, ip, ip] + [i32] * 7 + [fp, i32, i32, i32, vp]),
     "jl_attn_generic": (i32, [vp, vp, vp, vp, fp, i32, ip, ip] + [i32] * 7 + [f32, fp, i32, i32, vp]),
     "jl_attn_generic_splits": (i32, [i32, i32, i32, i32]),
     "jl_head_gate": (i32, [vp, fp, i32, i32, i32, i32, i32, vp]),
@@ -73,15 +73,25 @@ _HYBRID = {
     "jl_linear_tile_rows": (i32, []),
     "jl_linear_grouped": (i32, [vp, i32, i64, vp, i64, vp, i32, i64, i32, i32, i32, i32, i32, i32, f32, f32, ip, ip, ip, i32, i32,
                                 vp]),
-    "jl_attn_windowed": (i32, [vp, vp, vp, vp, ip, ip] + [i32] * 9 + [i64] * 4 + [i32, f32, fp, i32, i32, vp]),
+    "jl_attn_windowed": (i32, [vp, vp, vp, vp, ip, ip] + [i32] * 9 + [i64] * 4 + [i32, f32, fp, i32, i32, fp, i32, vp]),
     "jl_latent_prep": (i32, [fp] + [i32] * 8 + [vp, vp, vp, vp, fp, fp, i32, f32, ip, ip, i32, i32, i32, vp, vp, i32, vp]),
     "jl_rotary_slice": (i32, [vp, i32, i32, i32, vp, i32, i32, i32, i32, i32, i32, i32, fp, fp, i32, ip, ip, i32, i32, i32, vp]),
-    "jl_moe_route": (i32, [fp] + [i32] * 9 + [f32, ip, fp, vp]),
+    "jl_moe_route": (i32, [fp] + [i32] * 9 + [f32, fp, ip, fp, vp]),
     "jl_moe_sorted_rows": (i32, [i32, i32, i32]),
     "jl_moe_sort": (i32, [ip] + [i32] * 5 + [ip, ip, ip, ip, vp]),
     "jl_moe_gather": (i32, [vp, i32, ip, vp, i32, i32, i32, vp]),
     "jl_gemm_grouped": (i32, [vp, vp, vp, i32, i32, i32, i32, ip, ip, i32, i32, vp]),
     "jl_moe_combine": (i32, [fp, i32, ip, fp, i32, fp, i32, fp, i32, fp, i32, i32, vp]),
+    "jl_embed_pair_norm": (i32, [ip, vp, vp, vp, fp, ip, ip, ip] + [i32] * 5 + [i64, i64, f32, i32, vp]),
+    "jl_causal_conv": (i32, [fp, i32, i32, i32, vp, vp, fp, fp, i32, ip, ip] + [i32] * 5 + [vp]),
+    "jl_norm_mean2": (i32, [fp, i32, vp, fp, i32, vp, f32, fp, i32, i32, f32, i32, vp]),
+    "jl_gated_groupnorm": (i32, [fp, fp, i32, vp, i32, fp, i32, vp, vp, i32, i32, i32, f32, i32, i32, vp]),
+    "jl_glu_act": (i32, [fp, i32, i32, i32, vp, i32, i32, i32, i32, i32, f32, f32, ip, i32, i32, vp]),
+    "jl_talk_mix": (i32, [fp, vp, vp] + [i32] * 7 + [vp]),
+    "jl_ssd_gates": (i32, [fp, i32, i32, vp, vp, fp, i32, i32, i32, vp]),
+    "jl_ssd_scan": (i32, [fp, i32, i32, i32, i32, i32, fp, fp, fp, ip, ip] + [i32] * 5 + [fp, vp]),
+    "jl_delta_scan_ws_floats": (sz, [i32] * 5),
+    "jl_delta_scan": (i32, [fp, i32, i32, i32, i32, i32, fp, i32, i32, i32, vp, vp, vp, fp, fp, ip, ip] + [i32] * 6 + [fp, i32, vp]),
 }
 
 _OPTIONAL = {

@@ -16,9 +16,10 @@ import torch
 from . import _lib
 from .kernels import _p, _stream, ensure_gemm_workspace, num_sms
 
-ACT_NONE, ACT_RELU2, ACT_GELU_TANH, ACT_SILU, ACT_SCALE_SOFTCAP = 0, 1, 2, 3, 4
+ACT_NONE, ACT_RELU2, ACT_GELU_TANH, ACT_SILU, ACT_SCALE_SOFTCAP, ACT_SIGMOID = 0, 1, 2, 3, 4, 5
 GLA_FUSED_MAX_TOKENS = 8      # up to this many tokens per row the gated-linear-attention scan stays one fused launch
-ACTIVATIONS = {"none": ACT_NONE, "relu2": ACT_RELU2, "gelu_tanh": ACT_GELU_TANH, "silu": ACT_SILU}
+ACTIVATIONS = {"none": ACT_NONE, "relu2": ACT_RELU2, "gelu_tanh": ACT_GELU_TANH, "silu": ACT_SILU, "sigmoid": ACT_SIGMOID}
+GLU_PRODUCT, GLU_CLAMPED = 0, 1         # act(gate) * up;  g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit), u' = clamp(u, ±limit)
 
 
 def dtype_code(dtype: torch.dtype) -> int:
@@ -145,14 +146,19 @@ def linear(x: torch.Tensor, w: torch.Tensor, *, act: int = ACT_NONE, p0: float =
 def attn_prep(y: torch.Tensor, q_off: int, k_off: int, v_off: int, q_out: torch.Tensor,
               k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], cos: torch.Tensor, sin: torch.Tensor,
               rot: int, unit_norm: bool, eps: float, cache_len: torch.Tensor, pad_left: Optional[torch.Tensor],
-              B: int, S: int, H: int, G: int, D: int, Dv: int) -> None:
-    """Rotate / normalise q (and k), append k, v to the caches [B, G, T, D] / [B, G, T, Dv].  k_off < 0: queries only."""
+              B: int, S: int, H: int, G: int, D: int, Dv: int, bias: Optional[torch.Tensor] = None, v_unit_norm: bool = False,
+              v_token_major: bool = False) -> None:
+    """Rotate / normalise q (and k), append k, v to the caches [B, G, T, D] / [B, G, T, Dv].  k_off < 0: queries only.
+    bias: fp32 over the columns of y, added first; v_unit_norm: values scaled to unit RMS per head before they are cached;
+    v_token_major: the value cache is [B, T, G·Dv]."""
     _need(y, torch.float32, "y")
+    if bias is not None:
+        _need(bias, torch.float32, "bias")
     T_cap = k_cache.shape[2] if k_cache is not None else 0
     _lib.check(_lib.lib().jl_attn_prep(
         y.data_ptr(), y.stride(0), q_off, k_off, v_off, q_out.data_ptr(), _p(k_cache), _p(v_cache), cos.data_ptr(),
         sin.data_ptr(), cos.shape[0], rot, int(unit_norm), float(eps), _p(cache_len), _p(pad_left), B, S, H, G, D, Dv,
-        T_cap, dtype_code(q_out.dtype), _stream()), "jl_attn_prep")
+        T_cap, _p(bias), int(v_unit_norm), int(v_token_major), dtype_code(q_out.dtype), _stream()), "jl_attn_prep")
 
 
 def attn_generic(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, gate: Optional[torch.Tensor],
@@ -291,13 +297,16 @@ def rotary_slice(src: torch.Tensor, in_hs: int, in_off: int, out: torch.Tensor, 
 def attn_windowed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cache_len: torch.Tensor,
                   pad_left: Optional[torch.Tensor], B: int, S: int, H: int, G: int, D: int, Dv: int, T_cap: int, ldk: int,
                   ldv: int, window: int, scale: float, out: Optional[torch.Tensor] = None,
-                  strides: "tuple[int, int, int, int]" = (0, 0, 0, 0)) -> torch.Tensor:
+                  strides: "tuple[int, int, int, int]" = (0, 0, 0, 0), sink: bool = False, out_f32: bool = False
+                  ) -> torch.Tensor:
     """Causal attention of S new tokens per row over key / value rows of pitch ldk / ldv (keys and values may be
     columns of one cached row); window > 0 keeps the last `window` slots up to the query's own.  `strides`: elements
     between batch rows and between key/value heads for keys and for values — all zero: caches [B, G, T_cap, ·];
-    token-major projections [B·T, G, d] have (T·G·d, d) and a row pitch of G·d."""
+    token-major projections [B·T, G, d] have (T·G·d, d) and a row pitch of G·d.  sink: one more term exp(0) in the softmax
+    denominator (a key with score 0 and no value); out_f32: the result in fp32 whatever the operand type."""
     if out is None:
-        out = torch.empty((B * S, H * Dv), dtype=q.dtype, device=q.device)
+        out = torch.empty((B * S, H * Dv), dtype=torch.float32 if out_f32 else q.dtype, device=q.device)
+    f32_out = out.dtype == torch.float32 and q.dtype != torch.float32
     L = _lib.lib()
     splits, scratch = 0, None
     if S == 1:
@@ -305,9 +314,9 @@ def attn_windowed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
         if splits:
             scratch = torch.empty(B * H * splits * (Dv + 2), dtype=torch.float32, device=q.device)
     _lib.check(L.jl_attn_windowed(
-        q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), _p(cache_len), _p(pad_left), B, S, H, G, D, Dv,
-        T_cap, ldk, ldv, *(int(v) for v in strides), int(window), float(scale), _p(scratch), splits, dtype_code(q.dtype),
-        _stream()), "jl_attn_windowed")
+        q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), 0 if f32_out else out.data_ptr(), _p(cache_len), _p(pad_left),
+        B, S, H, G, D, Dv, T_cap, ldk, ldv, *(int(v) for v in strides), int(window), float(scale), _p(scratch), splits,
+        int(sink), out.data_ptr() if f32_out else 0, dtype_code(q.dtype), _stream()), "jl_attn_windowed")
     return out
 
 
@@ -334,14 +343,14 @@ def retention_scan(y: torch.Tensor, q_off: int, k_off: int, v_off: int, head_dec
 
 
 def moe_route(z: torch.Tensor, E: int, top: int, groups: int, keep: int, group_top: int, score: int, normalise: bool,
-              scale: float) -> "tuple[torch.Tensor, torch.Tensor]":
-    """fp32 router logits (columns 0..E-1 of z) → (experts int32 [M, top], weights fp32 [M, top])."""
+              scale: float, bias: Optional[torch.Tensor] = None) -> "tuple[torch.Tensor, torch.Tensor]":
+    """fp32 router logits (columns 0..E-1 of z, plus the fp32 `bias` [E]) → (experts int32 [M, top], weights fp32 [M, top])."""
     _need(z, torch.float32, "z")
     M = z.shape[0]
     idx = torch.empty((M, top), dtype=torch.int32, device=z.device)
     wt = torch.empty((M, top), dtype=torch.float32, device=z.device)
     _lib.check(_lib.lib().jl_moe_route(z.data_ptr(), z.stride(0), M, E, top, groups, keep, group_top, score, int(normalise),
-                                       float(scale), idx.data_ptr(), wt.data_ptr(), _stream()), "jl_moe_route")
+                                       float(scale), _p(bias), idx.data_ptr(), wt.data_ptr(), _stream()), "jl_moe_route")
     return idx, wt
 
 
@@ -403,4 +412,123 @@ def moe_combine(z: torch.Tensor, pos: Optional[torch.Tensor], wt: torch.Tensor, 
                                          shared.stride(0) if shared is not None else 0, _p(gate),
                                          gate.stride(0) if gate is not None else 0, out.data_ptr(), M, W, _stream()),
                "jl_moe_combine")
+    return out
+
+
+# --------------------------------------------------------------------------- pair-hash embedding, short convolutions, delta rule, state space
+def embed_pair_norm(ids: torch.Tensor, table: torch.Tensor, pair: torch.Tensor, norm_w: Optional[torch.Tensor],
+                    prev_tok: torch.Tensor, cache_len: Optional[torch.Tensor], pad_left: Optional[torch.Tensor], B: int, S: int,
+                    buckets: int, mul_prev: int, mul_cur: int, eps: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """norm(table[id] + pair[(prev · mul_prev + id · mul_cur) mod buckets]) · norm_w as fp32 [B·S, W]; a sequence's first token
+    takes row `buckets`; prev_tok int32 [B] carries the last token from call to call."""
+    ids32 = ids.to(torch.int32).contiguous().view(-1)
+    V, W = table.shape
+    if out is None:
+        out = torch.empty((B * S, W), dtype=torch.float32, device=table.device)
+    _lib.check(_lib.lib().jl_embed_pair_norm(ids32.data_ptr(), table.data_ptr(), pair.data_ptr(), _p(norm_w), out.data_ptr(),
+                                             prev_tok.data_ptr(), _p(cache_len), _p(pad_left), B, S, W, V, int(buckets),
+                                             int(mul_prev), int(mul_cur), float(eps), dtype_code(table.dtype), _stream()),
+               "jl_embed_pair_norm")
+    return out
+
+
+def causal_conv(y: torch.Tensor, col0: int, w: torch.Tensor, bias: Optional[torch.Tensor], state: Optional[torch.Tensor],
+                cache_len: Optional[torch.Tensor], pad_left: Optional[torch.Tensor], B: int, S: int, act: int = ACT_SILU,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """act(causal convolution over time) of the C = w.shape[0] columns of y (fp32) from col0; w [C, taps], the last tap on the
+    current token; state fp32 [B, taps-1, C]: the inputs before this call, replaced by this call's last."""
+    _need(y, torch.float32, "y")
+    C, taps = w.shape
+    if out is None:
+        out = torch.empty((B * S, C), dtype=torch.float32, device=y.device)
+    _lib.check(_lib.lib().jl_causal_conv(y.data_ptr(), y.stride(0), int(col0), C, w.data_ptr(), _p(bias), _p(state), out.data_ptr(),
+                                         out.stride(0), _p(cache_len), _p(pad_left), B, S, taps, act, dtype_code(w.dtype), _stream()),
+               "jl_causal_conv")
+    return out
+
+
+def norm_mean2(a: torch.Tensor, wa: torch.Tensor, b: Optional[torch.Tensor], wb: Optional[torch.Tensor], c: float, eps: float
+               ) -> torch.Tensor:
+    """c · (norm(a) · wa + norm(b) · wb), fp32 [M, W]."""
+    _need(a, torch.float32, "a")
+    M, W = a.shape
+    out = torch.empty((M, W), dtype=torch.float32, device=a.device)
+    _lib.check(_lib.lib().jl_norm_mean2(a.data_ptr(), a.stride(0), wa.data_ptr(), _p(b), b.stride(0) if b is not None else 0,
+                                        _p(wb), float(c), out.data_ptr(), M, W, float(eps), dtype_code(wa.dtype), _stream()),
+               "jl_norm_mean2")
+    return out
+
+
+def gated_groupnorm(o: torch.Tensor, x: Optional[torch.Tensor], skip: Optional[torch.Tensor], P: int, z: torch.Tensor,
+                    w: torch.Tensor, groups: int, eps: float, gate_act: int = ACT_SILU) -> torch.Tensor:
+    """((o + skip[head] · x) · act(z)) normed over each of `groups` equal parts of a row, times w; o fp32 [M, N]; x, z fp32 views."""
+    _need(o, torch.float32, "o")
+    M, N = o.shape
+    out = torch.empty((M, N), dtype=w.dtype, device=o.device)
+    _lib.check(_lib.lib().jl_gated_groupnorm(o.data_ptr(), _p(x), x.stride(0) if x is not None else 0, _p(skip), int(P),
+                                             z.data_ptr(), z.stride(0), w.data_ptr(), out.data_ptr(), M, N, int(groups),
+                                             float(eps), gate_act, dtype_code(w.dtype), _stream()), "jl_gated_groupnorm")
+    return out
+
+
+def glu_act(y: torch.Tensor, g_off: int, u_off: int, F: int, out_dtype: torch.dtype, *, kind: int = GLU_PRODUCT,
+            act: int = ACT_GELU_TANH, limit: float = 0.0, alpha: float = 1.0, rows_used: Optional[torch.Tensor] = None,
+            rows_mult: int = 1, zero: bool = False) -> torch.Tensor:
+    """Gated activation of the fp32 product y [M, gate | up] → [M, F] in `out_dtype`.  rows_used (device int): only the leading
+    rows_used · rows_mult rows are computed (`zero`: the rest reads as zero)."""
+    _need(y, torch.float32, "y")
+    M = y.shape[0]
+    out = (torch.zeros if zero else torch.empty)((M, F), dtype=out_dtype, device=y.device)
+    _lib.check(_lib.lib().jl_glu_act(y.data_ptr(), y.stride(0), int(g_off), int(u_off), out.data_ptr(), out.stride(0), M, F, kind,
+                                     act, float(limit), float(alpha), _p(rows_used), int(rows_mult), dtype_code(out_dtype), _stream()),
+               "jl_glu_act")
+    return out
+
+
+def talk_mix(o: torch.Tensor, mix: torch.Tensor, out: torch.Tensor, H: int, G: int, Gc: int, c0: int, Dv: int) -> torch.Tensor:
+    """out[m, h] = Σ_g mix[h, g] · o[m, g, kv(h) − c0] for the heads whose key/value head lies in [c0, c0 + Gc); o fp32."""
+    _need(o, torch.float32, "o")
+    _lib.check(_lib.lib().jl_talk_mix(o.data_ptr(), mix.data_ptr(), out.data_ptr(), out.shape[0], H, G, Gc, c0, Dv,
+                                      dtype_code(mix.dtype), _stream()), "jl_talk_mix")
+    return out
+
+
+def ssd_scan(y: torch.Tensor, dt_off: int, dt_bias: torch.Tensor, a_log: torch.Tensor, u: torch.Tensor, q_off: int, k_off: int,
+             v_off: int, G: int, state: torch.Tensor, cache_len: Optional[torch.Tensor], pad_left: Optional[torch.Tensor], B: int,
+             S: int, H: int, D: int, Dv: int) -> torch.Tensor:
+    """Selective state space scan: dt = softplus(y[:, dt_off + h] + dt_bias), S_t = exp(−exp(a_log) dt) S_(t−1) + dt k_t v_tᵀ,
+    o_t = S_tᵀ q_t with q / k (G groups of D, columns of u) shared by the heads of a group; state fp32 [B, H, D, Dv]."""
+    _need(y, torch.float32, "y")
+    _need(u, torch.float32, "u")
+    _need(state, torch.float32, "state")
+    M = B * S
+    L = _lib.lib()
+    aux = torch.empty((M, 2 * H), dtype=torch.float32, device=y.device)
+    _lib.check(L.jl_ssd_gates(y.data_ptr(), y.stride(0), int(dt_off), dt_bias.data_ptr(), a_log.data_ptr(), aux.data_ptr(), M, H,
+                              dtype_code(a_log.dtype), _stream()), "jl_ssd_gates")
+    out = torch.empty((M, H * Dv), dtype=torch.float32, device=y.device)
+    ws = None
+    if S > GLA_FUSED_MAX_TOKENS:
+        ws = torch.empty(int(L.jl_gla_scan_ws_floats(B, S, H, D, Dv)), dtype=torch.float32, device=y.device)
+    _lib.check(L.jl_ssd_scan(u.data_ptr(), u.stride(0), q_off, k_off, v_off, G, aux.data_ptr(), state.data_ptr(), out.data_ptr(),
+                             _p(cache_len), _p(pad_left), B, S, H, D, Dv, _p(ws), _stream()), "jl_ssd_scan")
+    return out
+
+
+def delta_scan(u: torch.Tensor, q_off: int, k_off: int, v_off: int, G: int, y: torch.Tensor, b_off: int, a_off: int,
+               a2: torch.Tensor, a_bias: torch.Tensor, a_log: torch.Tensor, state: torch.Tensor,
+               cache_len: Optional[torch.Tensor], pad_left: Optional[torch.Tensor], B: int, S: int, H: int, D: int, Dv: int
+               ) -> torch.Tensor:
+    """Gated delta rule over S tokens per row (see csrc/delta_scan.cu); returns the raw read-outs fp32 [B·S, H·Dv]."""
+    _need(u, torch.float32, "u")
+    _need(y, torch.float32, "y")
+    _need(state, torch.float32, "state")
+    L = _lib.lib()
+    R = a2.shape[1]
+    out = torch.empty((B * S, H * Dv), dtype=torch.float32, device=y.device)
+    ws = torch.empty(int(L.jl_delta_scan_ws_floats(B, S, H, D, Dv)), dtype=torch.float32, device=y.device)
+    _lib.check(L.jl_delta_scan(u.data_ptr(), u.stride(0), q_off, k_off, v_off, G, y.data_ptr(), y.stride(0), b_off, a_off,
+                               a2.data_ptr(), a_bias.data_ptr(), a_log.data_ptr(), state.data_ptr(), out.data_ptr(),
+                               _p(cache_len), _p(pad_left), B, S, H, D, Dv, R, ws.data_ptr(), dtype_code(a2.dtype), _stream()),
+               "jl_delta_scan")
     return out
