@@ -63,7 +63,7 @@ def causal_conv(x, w, bias=None):
 def sink_attention(h, t, p, m, eps):
     """The left half of a "parallel" mixer.  p: tensor prefix, m: its sizes."""
     T = h.shape[0]
-    H, G, D, Dv = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
+    H, G, D, Dv = int(m["heads"]), int(m.get("kv_heads", m["heads"])), int(m["dim"]), int(m["vdim"])
     window = int((m.get("mask") or {}).get("size") or 0)
     g = lambda n: t[p + n].to(F64)
     q = (h @ g("q").T + g("q.b")).view(T, H, D)
@@ -119,7 +119,7 @@ def parallel_mixer(h, t, p, m, eps):
 
 def channel_delta(h, t, p, m, eps):
     T = h.shape[0]
-    H, G, D, Dv = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
+    H, G, D, Dv = int(m["heads"]), int(m.get("kv_heads", m["heads"])), int(m["dim"]), int(m["vdim"])
     g = lambda n: t[p + n].to(F64)
     q = silu(causal_conv(h @ g("q").T, g("q.conv"))).view(T, G, D)
     k = silu(causal_conv(h @ g("k").T, g("k.conv"))).view(T, G, D)
