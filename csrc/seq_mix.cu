@@ -120,10 +120,12 @@ __global__ void __launch_bounds__(128) causal_conv_kernel(const float* __restric
   }
 }
 
-template <typename T>
+// One CTA per row; on the vector path (W a multiple of 4, 16-byte pitches, W <= 256 * 4 * VPT) both rows stay in registers
+// between the sums of squares and the output.
+template <typename T, int VPT>
 __global__ void __launch_bounds__(256) norm_mean2_kernel(const float* __restrict__ a, int lda, const T* __restrict__ wa,
                                                          const float* __restrict__ b, int ldb, const T* __restrict__ wb, float c,
-                                                         float* __restrict__ out, int W, float eps) {
+                                                         float* __restrict__ out, int W, float eps, int vec) {
   pdl_wait();                      // programmatic dependent launch: nothing is read before the predecessor is done
   pdl_launch_dependents();
   __shared__ float red[33];
@@ -131,6 +133,41 @@ __global__ void __launch_bounds__(256) norm_mean2_kernel(const float* __restrict
   const float* ar = a + m * lda;
   const float* br = b ? b + m * ldb : nullptr;
   float sa = 0.0f, sb = 0.0f;
+  if (vec) {
+    const int nv = W / 4;
+    float av[VPT][4], bv[VPT][4];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int idx = threadIdx.x + i * 256;
+      if (idx < nv) {
+        load4(ar + 4 * idx, av[i]);
+        if (br) load4(br + 4 * idx, bv[i]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { sa += av[i][j] * av[i][j]; if (br) sb += bv[i][j] * bv[i][j]; }
+      }
+    }
+    const float ra = 1.0f / sqrtf(block_sum(sa, red) / (float)W + eps);
+    const float rb = br ? 1.0f / sqrtf(block_sum(sb, red) / (float)W + eps) : 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int idx = threadIdx.x + i * 256;
+      if (idx < nv) {
+        float w4[4], o4[4];
+        load4(wa + 4 * idx, w4);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o4[j] = av[i][j] * ra * w4[j];
+        if (br) {
+          load4(wb + 4 * idx, w4);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) o4[j] += bv[i][j] * rb * w4[j];
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o4[j] *= c;
+        store4(out + m * W + 4 * idx, o4);
+      }
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
     const float u = ar[i];
     sa += u * u;
@@ -195,11 +232,10 @@ __global__ void __launch_bounds__(128) talk_mix_kernel(const float* __restrict__
   pdl_wait();                      // programmatic dependent launch: nothing is read before the predecessor is done
   pdl_launch_dependents();
   const size_t m = blockIdx.x;
-  const int per = H / G;
+  const int h = blockIdx.y, c = h / (H / G) - c0;          // grid (tokens, heads)
+  if (c < 0 || c >= Gc) return;
   const float* orow = o + m * H * Gc * Dv;
-  for (int i = threadIdx.x; i < H * Dv; i += blockDim.x) {
-    const int h = i / Dv, d = i % Dv, c = h / per - c0;
-    if (c < 0 || c >= Gc) continue;
+  for (int d = threadIdx.x; d < Dv; d += blockDim.x) {
     float acc = 0.0f;
     for (int g = 0; g < H; ++g) acc = fmaf(to_f(mix[h * H + g]), orow[((size_t)g * Gc + c) * Dv + d], acc);
     out[(m * H + h) * Dv + d] = from_f<T>(acc);
@@ -251,8 +287,14 @@ extern "C" JL_API int jl_causal_conv(const float* y, int ldy, int col0, int C, c
 extern "C" JL_API int jl_norm_mean2(const float* a, int lda, const void* wa, const float* b, int ldb, const void* wb, float c,
                                     float* out, int M, int W, float eps, int dtype, void* stream) {
   JL_CHECK_ARG(M >= 1 && W >= 1 && a != nullptr && wa != nullptr && (b == nullptr || wb != nullptr), "jl_norm_mean2: bad arguments");
-  JL_DISPATCH_DTYPE(dtype, JL_LAUNCH_PDL(norm_mean2_kernel<T>, dim3(M), dim3(256), 0, stream, a, lda, (const T*)wa, b, ldb,
-                                         (const T*)wb, c, out, W, eps));
+  const int vec = W % 4 == 0 && lda % 4 == 0 && ldb % 4 == 0 && ((uintptr_t)a | (uintptr_t)b | (uintptr_t)out) % 16 == 0 &&
+                  ((uintptr_t)wa | (uintptr_t)wb) % 16 == 0 && W <= 256 * 4 * 8;
+  if (vec && W <= 256 * 4 * 2)
+    JL_DISPATCH_DTYPE(dtype, JL_LAUNCH_PDL((norm_mean2_kernel<T, 2>), dim3(M), dim3(256), 0, stream, a, lda, (const T*)wa, b, ldb,
+                                           (const T*)wb, c, out, W, eps, 1));
+  else
+    JL_DISPATCH_DTYPE(dtype, JL_LAUNCH_PDL((norm_mean2_kernel<T, 8>), dim3(M), dim3(256), 0, stream, a, lda, (const T*)wa, b, ldb,
+                                           (const T*)wb, c, out, W, eps, vec));
   JL_CUDA(cudaGetLastError());
   return JL_OK;
 }
@@ -281,7 +323,7 @@ extern "C" JL_API int jl_glu_act(const float* in, int ldi, int g_off, int u_off,
 extern "C" JL_API int jl_talk_mix(const float* o, const void* mix, void* out, int M, int H, int G, int Gc, int c0, int Dv,
                                   int dtype, void* stream) {
   JL_CHECK_ARG(M >= 1 && H >= 1 && G >= 1 && H % G == 0 && Gc >= 1 && c0 >= 0 && c0 + Gc <= G && Dv >= 1, "jl_talk_mix: bad shape");
-  JL_DISPATCH_DTYPE(dtype, JL_LAUNCH_PDL(talk_mix_kernel<T>, dim3(M), dim3(128), 0, stream, o, (const T*)mix, (T*)out, H, G, Gc, c0, Dv));
+  JL_DISPATCH_DTYPE(dtype, JL_LAUNCH_PDL(talk_mix_kernel<T>, dim3(M, H), dim3(128), 0, stream, o, (const T*)mix, (T*)out, H, G, Gc, c0, Dv));
   JL_CUDA(cudaGetLastError());
   return JL_OK;
 }

@@ -58,21 +58,6 @@ __global__ void postnorm_add_kernel(const float* __restrict__ y, int ldy, const 
     h[(size_t)blockIdx.x * W + i] = from_f<T>(xr[i] * r2 * (offset + to_f(w_next[i])));
 }
 
-__device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
-  const float4 t = *reinterpret_cast<const float4*>(p);
-  v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
-}
-__device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&v)[4]) {
-  const uint2 t = *reinterpret_cast<const uint2*>(p);
-  v[0] = bf16_lo(t.x); v[1] = bf16_hi(t.x); v[2] = bf16_lo(t.y); v[3] = bf16_hi(t.y);
-}
-__device__ __forceinline__ void store4(float* p, const float (&v)[4]) {
-  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
-}
-__device__ __forceinline__ void store4(__nv_bfloat16* p, const float (&v)[4]) {
-  *reinterpret_cast<uint2*>(p) = make_uint2(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]));
-}
-
 // The same step with the row held in registers: 16-byte loads, x and y read once, x and h written once.
 // W % 4 == 0, ldy % 4 == 0, W <= 256 * 4 * VPT.
 template <typename T, int VPT>

@@ -542,10 +542,29 @@ class ParallelMixer(Mixer):
         got = [m.new_state(batch, device) for m in self.sides]
         return None if all(g is None for g in got) else tuple(got)
 
+    OVERLAP_ROWS = 8               # up to this many rows the two sides run on two streams
+
     def forward(self, h: torch.Tensor, B: int, S: int, cache: "object", layer: int, rope: Optional[Tuple] = None
                 ) -> torch.Tensor:
-        ys = [m.forward(h, B, S, _CacheView(cache, layer, i), layer, rope) for i, m in enumerate(self.sides)]
-        return SK.norm_mean2(ys[0], self.out_norms[0], ys[1], self.out_norms[1], self.spec.scale, self.eps)
+        """With a few rows (decoding) neither side fills the GPU and each is a chain of short dependent kernels, so the right
+        side runs on a second stream beside the left one (inside a graph capture the fork and join become edges of the
+        captured graph).  Prompts stay on one stream: their tensor-core GEMMs share one split-K workspace."""
+        views = [_CacheView(cache, layer, i) for i in range(2)]
+        if B * S <= self.OVERLAP_ROWS:
+            main = torch.cuda.current_stream()
+            if getattr(self, "_side", None) is None:
+                self._side, self._fork, self._join = torch.cuda.Stream(device=h.device), torch.cuda.Event(), torch.cuda.Event()
+            self._fork.record(main)
+            self._side.wait_event(self._fork)
+            with torch.cuda.stream(self._side):
+                right = self.sides[1].forward(h, B, S, views[1], layer, rope)
+                self._join.record(self._side)
+            left = self.sides[0].forward(h, B, S, views[0], layer, rope)
+            main.wait_event(self._join)
+        else:
+            left = self.sides[0].forward(h, B, S, views[0], layer, rope)
+            right = self.sides[1].forward(h, B, S, views[1], layer, rope)
+        return SK.norm_mean2(left, self.out_norms[0], right, self.out_norms[1], self.spec.scale, self.eps)
 
 
 MIXERS = {"attention": AttentionMixer, "gla": GlaMixer, "latent_attention": LatentAttentionMixer,

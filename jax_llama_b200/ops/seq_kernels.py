@@ -17,6 +17,7 @@ from . import _lib
 from .kernels import _p, _stream, ensure_gemm_workspace, num_sms
 
 ACT_NONE, ACT_RELU2, ACT_GELU_TANH, ACT_SILU, ACT_SCALE_SOFTCAP, ACT_SIGMOID = 0, 1, 2, 3, 4, 5
+DELTA_FUSED_MAX_TOKENS = 8    # the same for the delta-rule scan (csrc/delta_scan.cu DS_FUSED_MAX_TOKENS)
 GLA_FUSED_MAX_TOKENS = 8      # up to this many tokens per row the gated-linear-attention scan stays one fused launch
 ACTIVATIONS = {"none": ACT_NONE, "relu2": ACT_RELU2, "gelu_tanh": ACT_GELU_TANH, "silu": ACT_SILU, "sigmoid": ACT_SIGMOID}
 GLU_PRODUCT, GLU_CLAMPED = 0, 1         # act(gate) * up;  g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit), u' = clamp(u, ±limit)
@@ -526,9 +527,11 @@ def delta_scan(u: torch.Tensor, q_off: int, k_off: int, v_off: int, G: int, y: t
     L = _lib.lib()
     R = a2.shape[1]
     out = torch.empty((B * S, H * Dv), dtype=torch.float32, device=y.device)
-    ws = torch.empty(int(L.jl_delta_scan_ws_floats(B, S, H, D, Dv)), dtype=torch.float32, device=y.device)
+    ws = None
+    if S > DELTA_FUSED_MAX_TOKENS:        # prompts: token-parallel records + pipelined scan; fewer tokens: one fused launch
+        ws = torch.empty(int(L.jl_delta_scan_ws_floats(B, S, H, D, Dv)), dtype=torch.float32, device=y.device)
     _lib.check(L.jl_delta_scan(u.data_ptr(), u.stride(0), q_off, k_off, v_off, G, y.data_ptr(), y.stride(0), b_off, a_off,
                                a2.data_ptr(), a_bias.data_ptr(), a_log.data_ptr(), state.data_ptr(), out.data_ptr(),
-                               _p(cache_len), _p(pad_left), B, S, H, D, Dv, R, ws.data_ptr(), dtype_code(a2.dtype), _stream()),
+                               _p(cache_len), _p(pad_left), B, S, H, D, Dv, R, _p(ws), dtype_code(a2.dtype), _stream()),
                "jl_delta_scan")
     return out

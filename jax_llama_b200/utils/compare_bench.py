@@ -2,7 +2,8 @@
 random weights, plus the time of each kernel of the new design beside the like kernel of the other path:
 
 * ``bench.py --compare folirax`` — Folirax beside LLaMA (`run`),
-* ``bench.py --compare nikonex`` — Nikonex beside Folirax (`run_nikonex`).
+* ``bench.py --compare nikonex`` — Nikonex beside Folirax (`run_nikonex`),
+* ``bench.py --compare bazulorn`` — Bazulorn beside Nikonex (`run_bazulorn`).
 
 Everything is timed with CUDA events on the launching stream after warm-up; per-kernel timings flush L2 (a 256 MB write)
 between iterations, whole-model timings stream more weight bytes than L2 holds.  Fractions are of the measured peaks in
@@ -511,5 +512,265 @@ def run_nikonex(sizes: List[str], prompt_len: int = 2048, steps: int = 64, warmu
             torch.cuda.empty_cache()
         if kernels:
             entry["kernels"] = _nikonex_kernel_table(s, dev, peaks, prompt_len)
+        result["sizes"][name] = entry
+    return result
+
+
+# --------------------------------------------------------------------------------------------- Bazulorn beside Nikonex
+def bazulorn_config(s: Dict[str, int]) -> Any:
+    """[delta, parallel + experts, parallel + experts, delta + experts] × n at the head counts of the Nikonex shape: the
+    delta rule in place of retention (same 64 × 128 heads), windowed attention with 128-wide heads in place of latent
+    attention, a state space layer beside it, gated experts whose three matrices hold what Nikonex's two hold."""
+    from ..config import BazulornConfig
+
+    H = s["heads"]
+    dl = {"heads": H, "kv_heads": H, "dim": 64, "vdim": 128, "conv": 4}
+    pm = {"left": {"heads": H, "kv_heads": s["kv_heads"], "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                   "mask": {"size": s["window"]}},
+          "right": {"heads": H, "vdim": 64, "state": 128, "groups": 1, "conv": 4, "norm_groups": 1}}
+    ef, sf = s["expert_ff"] * 2 // 3 // 8 * 8, s["shared_ff"] * 2 // 3 // 8 * 8
+    mlp = {"kind": "moe", "expert": {"ff": ef, "limit": 7.0}, "shared": {"ff": sf, "limit": 7.0},
+           "router": {"experts": s["experts"], "top": s["top"]}}
+    block = [("channel_delta", dl, None), ("parallel", pm, mlp), ("parallel", pm, mlp), ("channel_delta", dl, mlp)]
+    layers = [{"type": block[i % 4][0], "mixer": block[i % 4][1], "mlp": block[i % 4][2]} for i in range(s["layers"])]
+    return BazulornConfig.from_dict({"architecture": "Bazulorn", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-5},
+                                     "embedding": {"bigram": {"buckets": 65521, "mul_prev": 1000003, "mul_cur": 7919}},
+                                     "layers": layers})
+
+
+def _bazulorn_kernel_table(s: Dict[str, int], dev: torch.device, peaks: Dict[str, float], prompt_len: int) -> List[Dict[str, Any]]:
+    """Each kernel that Bazulorn adds, at this size, beside the like kernel of the Nikonex path: ms, achieved rate, the
+    fraction of the measured roofline, and how much farther from it the new kernel is (`distance_ratio`)."""
+    from ..config import MoeMlpSpec
+    from ..models.feedforward import MoeFeedForward
+    from ..models.mixers import rotary_table
+    from ..ops import seq_kernels as SK
+
+    t = Timer(dev)
+    hbm, tf = peaks["hbm_gbs"], peaks["bf16_tflops"]
+    W, H, G = s["width"], s["heads"], s["kv_heads"]
+    E, top = s["experts"], s["top"]
+    ef, nef = s["expert_ff"] * 2 // 3 // 8 * 8, s["expert_ff"]
+    win, P = s["window"], prompt_len
+    D = Dv = 128
+    gd, gv, N, sv, R = 64, 128, 128, 64, 16
+    bf = dict(dtype=torch.bfloat16, device=dev)
+    rows: List[Dict[str, Any]] = []
+
+    def add(name: str, ms: float, like: str, like_ms: float, nbytes: float = 0.0, flops: float = 0.0, like_nbytes: float = 0.0,
+            like_flops: float = 0.0, note: str = "") -> None:
+        r: Dict[str, Any] = {"kernel": name, "ms": round(ms, 4), "like": like, "like_ms": round(like_ms, 4) if like_ms else None}
+        frac = like_frac = None
+        if nbytes:
+            r["gbs"] = round(nbytes / ms / 1e6, 1)
+            frac = nbytes / ms / 1e6 / hbm
+            r["frac_hbm_of_measured"] = round(frac, 4)
+            if like_ms:
+                like_frac = (like_nbytes or nbytes) / like_ms / 1e6 / hbm
+        if flops:
+            r["tflops"] = round(flops / ms / 1e9, 2)
+            frac = flops / ms / 1e9 / tf
+            r["frac_bf16_of_measured"] = round(frac, 5)
+            if like_ms:
+                like_frac = (like_flops or flops) / like_ms / 1e9 / tf
+        if like_frac is not None:
+            r["like_frac"] = round(like_frac, 5)
+            r["distance_ratio"] = round(like_frac / frac, 2)
+        if note:
+            r["note"] = note
+        rows.append(r)
+
+    zero = torch.zeros(1, dtype=torch.int32, device=dev)
+    pad = torch.zeros(1, dtype=torch.int32, device=dev)
+    pad8 = torch.zeros(8, dtype=torch.int32, device=dev)
+    ctx_len = torch.full((1,), P, dtype=torch.int32, device=dev)
+    T = P + 8
+
+    # ---- embedding: token row + hashed pair row + norm, beside the plain lookup
+    V = s["vocab"]
+    emb, pair, wn = torch.randn(V, W, **bf), torch.randn(65522, W, **bf), torch.ones(W, **bf)
+    ids = torch.randint(0, V, (P,), dtype=torch.int32, device=dev)
+    prev = torch.zeros(1, dtype=torch.int32, device=dev)
+    add("embed_pair_norm (two table rows, norm)",
+        t.kernel(lambda: SK.embed_pair_norm(ids, emb, pair, wn, prev, zero, pad, 1, P, 65521, 1000003, 7919, 1e-5)),
+        "embed_f32 (one table row)", t.kernel(lambda: SK.embed_f32(ids, emb)), nbytes=P * W * 8.0, like_nbytes=P * W * 6.0)
+
+    # ---- the norms around two mixers side by side, beside the block's residual step
+    x, y1, y2 = (torch.randn(P, W, device=dev) for _ in range(3))
+    w1, w2 = torch.ones(W, **bf), torch.ones(W, **bf)
+    add("norm_mean2 (two branch norms, half their sum)", t.kernel(lambda: SK.norm_mean2(y1, w1, y2, w2, 0.5, 1e-5)),
+        "branch_add_norm (two branches, two norms)", t.kernel(lambda: SK.branch_add_norm(x, y1, y2, 0.5, w1, w2, 1e-5)),
+        nbytes=P * W * 12.0, like_nbytes=P * W * 20.0)
+
+    # ---- short convolutions (prompt and one token x 8 rows), beside the preparation kernel of latent attention
+    C = 2 * H * gd + H * gv
+    yc = torch.randn(P, C + H + 2 * R + 8, device=dev)
+    cw = torch.randn(C, 4, **bf)
+    cst = torch.zeros(1, 3, C, device=dev)
+    qr, rank, Rr = s["q_rank"], s["kv_rank"], 64
+    cos, sin = rotary_table(Rr, 10000.0, T, dev)
+    yl = torch.randn(P, qr + rank + Rr, device=dev)
+    wqn, wkn = torch.ones(qr, **bf), torch.ones(rank, **bf)
+    lcache = torch.zeros(1, T, rank + Rr, **bf)
+    add("causal_conv + silu (q | k | v of the delta rule, prompt)", t.kernel(lambda: SK.causal_conv(yc, 0, cw, None, cst, zero, pad, 1, P)),
+        "latent_prep (two norms, rotation, append)",
+        t.kernel(lambda: SK.latent_prep(yl, 0, qr, qr, rank, Rr, Rr, 0, wqn, wkn, lcache, cos, sin, 1e-5, zero, pad, 1, P)),
+        nbytes=P * C * 8.0, like_nbytes=P * (qr + rank + Rr) * 6.0)
+
+    # ---- recurrences: delta rule and state space scan beside retention (prompt; one token x 8 rows)
+    u = torch.randn(P, C, device=dev) * 0.3
+    yb = torch.randn(P, H + R + 8, device=dev) * 0.3
+    a2 = torch.randn(H * gd, R, **bf) * 0.1
+    ab = torch.full((H * gd,), 0.5, **bf)
+    al = torch.full((H,), -3.0, **bf)
+    dstate = torch.zeros(1, H, gd, gv, device=dev)
+    yr = torch.randn(P, 2 * H * gd + 2 * H * gv, device=dev) * 0.3
+    rstate = torch.zeros(1, H, gd, gv, device=dev)
+    decay = torch.linspace(0.97, 0.999, H, device=dev)
+    rc, rs = rotary_table(gd, 10000.0, T, dev)
+    ms_ret = t.kernel(lambda: SK.retention_scan(yr, 0, H * gd, 2 * H * gd, decay, rc, rs, gd, 1, gd ** -0.5, rstate, zero, pad, 1, P,
+                                                H, gd, gv), reps=5)
+    state_fl = 4.0 * P * H * gd * gv
+    add("delta rule scan (prompt: token-parallel preparation + sequential scan)",
+        t.kernel(lambda: SK.delta_scan(u, 0, H * gd, 2 * H * gd, H, yb, 0, H, a2, ab, al, dstate, zero, pad, 1, P, H, gd, gv), reps=5),
+        "retention scan (prompt, time chunks)", ms_ret, flops=1.5 * state_fl, like_flops=state_fl,
+        note="the correction multiplies the state by (I - beta k k^T): no chunk-parallel two-pass form; fractions are of the "
+             "tensor-core peak and only rank the two")
+    inner, gn = H * sv, N
+    us = torch.randn(P, inner + 2 * gn, device=dev) * 0.3
+    ys = torch.randn(P, 2 * inner + 2 * gn + H, device=dev) * 0.3
+    dtb, sal = torch.zeros(H, **bf), torch.full((H,), -3.0, **bf)
+    sstate = torch.zeros(1, H, N, sv, device=dev)
+    add("state space scan (prompt; the gated-linear-attention kernels with per-token decays)",
+        t.kernel(lambda: SK.ssd_scan(ys, 2 * inner + 2 * gn, dtb, sal, us, inner + gn, inner, 0, 1, sstate, zero, pad, 1, P, H, N, sv),
+                 reps=5),
+        "retention scan (prompt, time chunks)", ms_ret, flops=4.0 * P * H * N * sv, like_flops=state_fl)
+    u8, yb8 = u[:8].contiguous(), yb[:8].contiguous()
+    d8 = torch.zeros(8, H, gd, gv, device=dev)
+    r8 = torch.zeros(8, H, gd, gv, device=dev)
+    yr8 = yr[:8].contiguous()
+    add("delta rule scan, one token x 8 rows (two launches)",
+        t.kernel(lambda: SK.delta_scan(u8, 0, H * gd, 2 * H * gd, H, yb8, 0, H, a2, ab, al, d8, ctx_len, pad8, 8, 1, H, gd, gv)),
+        "retention scan, one token x 8 rows (one launch)",
+        t.kernel(lambda: SK.retention_scan(yr8, 0, H * gd, 2 * H * gd, decay, rc, rs, gd, 1, gd ** -0.5, r8, ctx_len, pad8, 8, 1, H,
+                                           gd, gv)),
+        nbytes=8.0 * H * gd * gv * 8.0)
+
+    # ---- attention: preparation, prompt and one token with mixed head weights, beside Nikonex's windowed attention
+    n_qkv = (H + 2 * G) * D
+    yq = torch.randn(P, n_qkv + 8, device=dev) * 0.3
+    bias = torch.zeros(n_qkv + 8, device=dev)
+    qo = torch.empty(P, H * D, **bf)
+    kc, vtm = torch.zeros(1, G, T, D, **bf), torch.zeros(1, T, G * Dv, **bf)
+    kc2, vc2 = torch.zeros(1, G, T, D, **bf), torch.zeros(1, G, T, Dv, **bf)
+    one = torch.ones(1, 1, device=dev)
+    add("attn_prep (biases, unit-RMS values, append; no rotation)",
+        t.kernel(lambda: SK.attn_prep(yq, 0, H * D, (H + G) * D, qo, kc, vtm, one, one, 0, False, 1e-5, zero, pad, 1, P, H, G, D, Dv,
+                                      bias=bias, v_unit_norm=True, v_token_major=True)),
+        "attn_prep (rotation, unit norm, append)",
+        t.kernel(lambda: SK.attn_prep(yq, 0, H * D, (H + G) * D, qo, kc2, vc2, cos, sin, 64, True, 1e-5, zero, pad, 1, P, H, G, D, Dv)),
+        nbytes=P * n_qkv * 6.0)
+    kc.normal_()
+    vtm.normal_()
+    qf = torch.randn(P, H * D, **bf) * 0.05
+    win_keys = sum(min(i + 1, win) for i in range(P))
+    qd = D + 64
+    qn = torch.randn(P, H * qd, **bf) * 0.05
+    kn = torch.randn(P, H * qd, **bf) * 0.05
+    vn = torch.randn(P, H * Dv, **bf)
+    talk = torch.randn(H, H, **bf) * 0.1
+    mixed = torch.empty(P, H * Dv, **bf)
+
+    def attend(S: int, q: torch.Tensor, length: torch.Tensor, out: torch.Tensor) -> None:
+        per = max(1, 512 // Dv)
+        for c0 in range(0, G, per):
+            gc = min(per, G - c0)
+            o = SK.attn_windowed(q, kc, vtm[:, :, c0 * Dv:], length, pad, 1, S, H, G, D, gc * Dv, T, D, G * Dv, win, D ** -0.5,
+                                 strides=(G * T * D, T * D, T * G * Dv, 0), sink=True, out_f32=True)
+            SK.talk_mix(o, talk, out, H, G, gc, c0, Dv)
+
+    add("attention with mixed head weights (prompt): attn_rows over all value heads + talk_mix",
+        t.kernel(lambda: attend(P, qf, zero, mixed), reps=3),
+        "attn_rows_kernel, windowed, per-head keys (prompt, Nikonex)",
+        t.kernel(lambda: SK.attn_windowed(qn, kn, vn, zero, pad, 1, P, H, H, qd, Dv, P, H * qd, H * Dv, win, 192 ** -0.5,
+                                          strides=(P * H * qd, qd, P * H * Dv, Dv)), reps=3),
+        flops=2.0 * H * win_keys * (D + G * Dv), like_flops=2.0 * H * win_keys * (qd + Dv),
+        note="every query head weighs the values of all key/value heads, so that the mix across heads is a small product "
+             "afterwards; the same exact SIMT kernel on both sides")
+    q1 = qf[:1].contiguous()
+    m1 = torch.empty(1, H * Dv, **bf)
+    row = rank + Rr
+    q1l = torch.randn(1, H * row, **bf) * 0.05
+    add("attention with mixed head weights (one token): attn_split + attn_merge + talk_mix",
+        t.kernel(lambda: attend(1, q1, ctx_len, m1)), "attn_split + attn_merge, windowed latent rows (one token, Nikonex)",
+        t.kernel(lambda: SK.attn_windowed(q1l, lcache, lcache, ctx_len, pad, 1, 1, H, 1, row, rank, T, row, row, win, 192 ** -0.5)),
+        nbytes=min(win, P) * G * (D + Dv) * 2.0, like_nbytes=min(win, P) * row * 2.0)
+
+    # ---- gated read-outs
+    o = torch.randn(P, H * gv, device=dev)
+    gate = torch.randn(P, H * gv, device=dev)
+    wv = torch.ones(gv, **bf)
+    wfull = torch.ones(H * gv, **bf)
+    skip = torch.ones(H, **bf)
+    add("gated_groupnorm ((o + D x) silu(z), norm, weight)",
+        t.kernel(lambda: SK.gated_groupnorm(o, gate, skip, gv, gate, wfull, 1, 1e-5)),
+        "headnorm_gate (norm per head, silu gate)", t.kernel(lambda: SK.headnorm_gate(o, wv, gate, H, gv, 1e-5, SK.ACT_SILU)),
+        nbytes=P * H * gv * 14.0, like_nbytes=P * H * gv * 10.0)
+
+    # ---- experts: prompt and one token, beside Nikonex's experts of equal parameter count
+    hp = torch.randn(P, W, **bf)
+    torch.manual_seed(0)
+
+    def make(gated: bool) -> MoeFeedForward:
+        f = ef if gated else nef
+        spec = MoeMlpSpec(experts=E, top=top, ff=f, act="glu_clamped" if gated else "relu2", score="softmax" if gated else "sigmoid",
+                          shared_ff=0, shared_gate=False, gated=gated, limit=7.0, router_bias=gated)
+        w = {"router": torch.randn(E, W, **bf) * 0.02}
+        if gated:
+            w["router.b"] = torch.zeros(E, **bf)
+        for e in range(E):
+            w[f"e{e}.up"], w[f"e{e}.down"] = torch.randn(f, W, **bf) * 0.02, torch.randn(W, f, **bf) * 0.02
+            if gated:
+                w[f"e{e}.gate"] = torch.randn(f, W, **bf) * 0.02
+        return MoeFeedForward(spec, w)
+
+    new, old = make(True), make(False)
+    fl_new, fl_old = 2.0 * P * top * 3 * ef * W, 2.0 * P * top * 2 * nef * W
+    add("gated experts, prompt (router, sort, gather, grouped tcgen05 GEMM, gated activation, grouped GEMM, combine)",
+        t.kernel(lambda: new.run(hp), reps=5), "experts, prompt (Nikonex: the same chain with relu² in place)",
+        t.kernel(lambda: old.run(hp), reps=5), flops=fl_new, like_flops=fl_old)
+    h1 = hp[:1].contiguous()
+    add("gated experts, one token (router, choice, gate | up stream, gated activation, down stream, combine)",
+        t.kernel(lambda: new.run(h1)), "experts, one token (Nikonex)", t.kernel(lambda: old.run(h1)),
+        nbytes=top * 3.0 * ef * W * 2, like_nbytes=top * 2.0 * nef * W * 2, note="six launches against five")
+    return rows
+
+
+def run_bazulorn(sizes: List[str], prompt_len: int = 2048, steps: int = 64, warmup: int = 8, batches: List[int] = (1, 8),
+                 kernels: bool = True) -> Dict[str, Any]:
+    """Bazulorn beside the closest existing design, Nikonex, at equal width, depth, head counts and expert parameters."""
+    from ..models.hybrid_engine import HybridEngine
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    try:
+        with open(os.path.join(root, "MEASURED_PEAKS.json")) as f:
+            m = json.load(f)
+        peaks = {"hbm_gbs": float(m["hbm_gbs"]), "bf16_tflops": float(m["bf16_tflops"]), "source": "measured"}
+    except (OSError, KeyError, ValueError):
+        pass
+    result: Dict[str, Any] = {"metric": "bazulorn_vs_nikonex_equal_size", "data": "synthetic", "dtype": "bf16", "peaks": peaks,
+                              "prompt_len": prompt_len, "steps": steps, "warmup": warmup, "sizes": {}}
+    for name in sizes:
+        s = NIKONEX_SIZES[name]
+        entry: Dict[str, Any] = {"shape": s}
+        for label, cfg in (("bazulorn", bazulorn_config(s)), ("nikonex", nikonex_config(s))):
+            eng = HybridEngine.random_init(cfg, dev, seed=0)
+            entry[label] = _model_times(eng, s["vocab"], prompt_len, list(batches), steps, warmup)
+            del eng
+            torch.cuda.empty_cache()
+        if kernels:
+            entry["kernels"] = _bazulorn_kernel_table(s, dev, peaks, prompt_len)
         result["sizes"][name] = entry
     return result
