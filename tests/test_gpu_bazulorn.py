@@ -222,6 +222,7 @@ SINGLE = {
     "delta_alone": [delta()],
     "delta_one_qk_head_wide_keys": [delta(heads=3, kv_heads=1, dim=80, vdim=10, conv=2)],
     "delta_key_of_33": [delta(heads=2, kv_heads=2, dim=33, vdim=7, conv=1)],
+    "delta_keys_above_256": [delta(heads=1, kv_heads=1, dim=264, vdim=6, conv=2)],
     "attention_and_state_space": [par()],
     "one_kv_head_window_one": [par(heads=4, kv_heads=1, dim=8, vdim=16, window=1, s_heads=2, groups=2, norm_groups=4)],
     "no_window_one_group": [par(heads=2, kv_heads=2, dim=24, vdim=8, window=0, s_heads=6, s_vdim=4, state=40, groups=1, conv=3,
@@ -371,6 +372,13 @@ def test_odd_sizes_and_a_batch_of_twenty(dtype):
               delta(heads=3, kv_heads=1, dim=12, vdim=10, conv=2, mlp=moe(experts=3, top=1, ff=5, shared=0))]
     cfg = config(layers, vocab=77, width=90, dtype=dtype)
     run_unequal_batch(cfg, dtype, [3, 17, 1, 9, 30, 2, 12, 25, 8, 21, 4, 5, 6, 7, 11, 13, 14, 15, 16, 29], 12, seed=17)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_delta_rule_in_a_grid_that_fills_the_gpu(dtype):
+    """Twenty rows of 64 x 64 heads: the scan then keeps 32 key channels per thread instead of 8 (prompt and decoding)."""
+    cfg = config([delta(heads=4, kv_heads=2, dim=64, vdim=64, mlp=dense(ff=24))], dtype=dtype)
+    run_unequal_batch(cfg, dtype, [3, 17, 1, 9, 30, 2, 12, 25, 8, 21, 4, 5, 6, 7, 11, 13, 14, 15, 16, 29], 10, seed=19)
 
 
 def test_realistic_head_sizes():
