@@ -710,5 +710,5 @@ class BazulornConfig(HybridConfig):
 
     def validate(self) -> None:
         super().validate()
-        if self.pair_embedding is None or self.pair_embedding.buckets <= 0:
-            raise ValueError("embedding.bigram {buckets, mul_prev, mul_cur} is required")
+        if self.pair_embedding is not None and self.pair_embedding.buckets <= 0:
+            raise ValueError("embedding.bigram.buckets must be positive")

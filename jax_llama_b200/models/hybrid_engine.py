@@ -179,6 +179,12 @@ class HybridEngine(B200Engine):
         self.lm_head = self.embedding if config.tied_head else get("head")
         self.embed_norm = get("embed.norm") if config.embed_norm else None
         self.pair_table = get("bigram") if config.pair_embedding is not None else None
+        self.pair_spec = config.pair_embedding
+        if self.pair_table is None and self.embed_norm is not None:
+            # a normed embedding without a pair table runs the same kernel over a table of zeros
+            from ..config import PairEmbeddingSpec
+            self.pair_table = torch.zeros((2, config.hidden_size), dtype=dtype, device=self.device)
+            self.pair_spec = PairEmbeddingSpec(buckets=1, mul_prev=0, mul_cur=0)
         self.v_local = config.vocab_size
         self.layers: List[HybridLayer] = []
         for i, l in enumerate(config.layers):
@@ -270,15 +276,12 @@ class HybridEngine(B200Engine):
     def _embed(self, ids: torch.Tensor, out: Optional[torch.Tensor] = None, cache: Optional[HybridCache] = None,
                B: int = 0, S: int = 0) -> torch.Tensor:
         if self.pair_table is not None:
-            pe = self.config.pair_embedding
+            pe = self.pair_spec
             if cache is None or cache.prev_tok is None:
                 raise ValueError("an embedding that hashes token pairs needs the cache of the request batch")
             return SK.embed_pair_norm(ids, self.embedding, self.pair_table, self.embed_norm, cache.prev_tok, cache.len_dev,
                                       cache.pad_left, B, S, pe.buckets, pe.mul_prev, pe.mul_cur, self.eps, out=out)
-        x = SK.embed_f32(ids, self.embedding, out=out)
-        if self.embed_norm is not None:
-            raise NotImplementedError("a norm after a plain embedding")
-        return x
+        return SK.embed_f32(ids, self.embedding, out=out)
 
     def _head(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         c = self.config

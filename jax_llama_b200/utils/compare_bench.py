@@ -649,7 +649,7 @@ def _bazulorn_kernel_table(s: Dict[str, int], dev: torch.device, peaks: Dict[str
     d8 = torch.zeros(8, H, gd, gv, device=dev)
     r8 = torch.zeros(8, H, gd, gv, device=dev)
     yr8 = yr[:8].contiguous()
-    add("delta rule scan, one token x 8 rows (two launches)",
+    add("delta rule scan, one token x 8 rows (one fused launch)",
         t.kernel(lambda: SK.delta_scan(u8, 0, H * gd, 2 * H * gd, H, yb8, 0, H, a2, ab, al, d8, ctx_len, pad8, 8, 1, H, gd, gv)),
         "retention scan, one token x 8 rows (one launch)",
         t.kernel(lambda: SK.retention_scan(yr8, 0, H * gd, 2 * H * gd, decay, rc, rs, gd, 1, gd ** -0.5, r8, ctx_len, pad8, 8, 1, H,

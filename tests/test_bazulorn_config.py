@@ -65,7 +65,7 @@ def test_config_defaults_and_validation():
                 lambda d: d["layers"][0]["mixer"].update(kv_heads=3),
                 lambda d: d["layers"][1]["mlp"]["router"].update(top=7),
                 lambda d: d["layers"][0].update(type="retention"),
-                lambda d: d.pop("embedding")):
+                lambda d: d["embedding"]["bigram"].update(buckets=0)):
         e = cfg_dict()
         bad(e)
         with pytest.raises((ValueError, KeyError)):
