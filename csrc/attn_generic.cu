@@ -38,6 +38,11 @@ struct PrepParams {
   const float* bias;                // fp32, indexed like the columns of y (added before anything else), or nullptr
   int v_norm;                       // values scaled to unit RMS per head (no weight) before they are cached
   int v_token_major;                // value cache [B][T][G*Dv] (all heads of a token in one row) instead of [B][G][T][Dv]
+  int layout;                       // pairing of the rotated q / k channels: 0 = (2i, 2i+1), 1 = (i, i + rot/2)
+  const void* qw; const void* kw;   // [D] weights (element type of the caches) of an RMS norm of every q / k head BEFORE the
+                                    // rotation, shared by the heads; nullptr: none
+  const float* vcos; const float* vsin; int v_max_pos, v_layout;   // [v_max_pos][Dv/2]: values are rotated at their own position over all
+                                    // Dv channels before they are cached (pairs as v_layout says); nullptr: cached as they are
 };
 
 constexpr int AP_WARPS = 4;      // heads per CTA of the preparation kernel (one warp each)
@@ -64,6 +69,21 @@ __global__ void __launch_bounds__(AP_WARPS * 32) attn_prep_kernel(PrepParams p, 
       for (int i = lane; i < p.Dv; i += 32) { const float v = yr[p.v_off + g * p.Dv + i] + (vb ? vb[i] : 0.0f); ss += v * v; }
       r = 1.0f / sqrtf(warp_sum(ss) / (float)p.Dv + p.eps);
     }
+    if (p.vcos) {                                          // value turned by its own position (undone on the head's sum later)
+      int vpos = slot - (p.pad_left ? p.pad_left[b] : 0);
+      vpos = vpos < 0 ? 0 : (vpos >= p.v_max_pos ? p.v_max_pos - 1 : vpos);
+      const float* ct = p.vcos + (size_t)vpos * (p.Dv / 2);
+      const float* st = p.vsin + (size_t)vpos * (p.Dv / 2);
+      const float* vs = yr + p.v_off + g * p.Dv;
+      const int half = p.Dv / 2;
+      for (int i = lane; i < half; i += 32) {
+        const int c0 = p.v_layout ? i : 2 * i, c1 = p.v_layout ? i + half : 2 * i + 1;
+        const float u = (vs[c0] + (vb ? vb[c0] : 0.0f)) * r, v = (vs[c1] + (vb ? vb[c1] : 0.0f)) * r;
+        dst[c0] = from_f<T>(u * ct[i] - v * st[i]);
+        dst[c1] = from_f<T>(v * ct[i] + u * st[i]);
+      }
+      return;
+    }
     for (int i = lane; i < p.Dv; i += 32) dst[i] = from_f<T>((yr[p.v_off + g * p.Dv + i] + (vb ? vb[i] : 0.0f)) * r);
     return;
   }
@@ -75,6 +95,26 @@ __global__ void __launch_bounds__(AP_WARPS * 32) attn_prep_kernel(PrepParams p, 
                 : kc + (((size_t)b * p.G + (head - p.H)) * p.T + slot) * p.D;
   const float* ct = p.cos_t + (size_t)pos * (p.rot / 2);
   const float* st = p.sin_t + (size_t)pos * (p.rot / 2);
+  if (p.qw != nullptr || p.layout != 0) {
+    // general form: optional RMS norm with a weight first, then the rotation in either pairing
+    const T* w = reinterpret_cast<const T*>(is_q ? p.qw : p.kw);
+    float r = 1.0f;
+    if (w) {
+      float ss = 0.0f;
+      for (int c = lane; c < p.D; c += 32) { const float v = src[c] + (bs ? bs[c] : 0.0f); ss += v * v; }
+      r = 1.0f / sqrtf(warp_sum(ss) / (float)p.D + p.eps);
+    }
+    auto val = [&](int c) { const float v = src[c] + (bs ? bs[c] : 0.0f); return w ? v * r * to_f(w[c]) : v; };
+    const int half = p.rot / 2;
+    for (int i = lane; i < half; i += 32) {
+      const int c0 = p.layout ? i : 2 * i, c1 = p.layout ? i + half : 2 * i + 1;
+      const float u = val(c0), v = val(c1);
+      dst[c0] = from_f<T>(u * ct[i] - v * st[i]);
+      dst[c1] = from_f<T>(v * ct[i] + u * st[i]);
+    }
+    for (int c = p.rot + lane; c < p.D; c += 32) dst[c] = from_f<T>(val(c));
+    return;
+  }
   const int npairs = p.D / 2 + (p.D & 1);
   // pass 1 rotates and sums the squares, pass 2 rotates again (L1 hits) and writes the scaled values
   float r = 1.0f;
@@ -187,16 +227,49 @@ struct AttnParams {
   const float* gate; int ldg;       // fp32 pre-activation of the per-head output gate (column h of row m), or nullptr
   int sink;                         // 1: the softmax denominator has one more term exp(0) (a key with score 0 and no value)
   float* out32;                     // fp32 output [M][H][Dv] instead of `out` (what a later fp32 step reads), or nullptr
+  int chunk;                        // > 0: positions (slot - pad_left) form blocks of `chunk`; a query sees the keys of its own block only
+  const float* sink_logit;          // [H] fp32: the extra term of the denominator is exp(sink_logit[h]) instead of exp(0) (with sink = 1)
+  const float* vcos; const float* vsin; int v_max_pos, v_layout;   // [v_max_pos][Dv/2]: the cached values were rotated at their own
+                                    // positions; every head's sum is rotated back by the query's position (pairs as v_layout)
 };
 
+// first slot a query at slot hi_q of a row whose sequence starts at slot lo may see
+__device__ __forceinline__ int attn_first_visible(const AttnParams& p, int lo, int hi_q) {
+  int first = lo;
+  if (p.window > 0) first = max(first, hi_q - p.window + 1);
+  if (p.chunk > 0 && hi_q >= lo) first = max(first, lo + (hi_q - lo) / p.chunk * p.chunk);
+  return first;
+}
+
 // the denominator of a row whose running maximum is m and whose visible keys sum to l (l == 0: nothing visible, the row is zero)
-__device__ __forceinline__ float attn_inv_denominator(const AttnParams& p, float m, float l) {
+__device__ __forceinline__ float attn_inv_denominator(const AttnParams& p, float m, float l, int h) {
   if (!(l > 0.0f)) return 0.0f;
-  return 1.0f / (p.sink ? l + expf(-m) : l);
+  return 1.0f / (p.sink ? l + expf((p.sink_logit ? p.sink_logit[h] : 0.0f) - m) : l);
 }
 template <typename T>
 __device__ __forceinline__ void attn_store(const AttnParams& p, T* out, size_t at, float v) {
   if (p.out32) p.out32[at] = v; else out[at] = from_f<T>(v);
+}
+
+// A head's normalised sum `o` (Dv floats in shared memory, complete and visible to the calling threads) → rotated back by the
+// query's position when the values were cached rotated, times gmul, stored.  Threads tid, tid + nthreads, ... take the columns.
+template <typename T>
+__device__ __forceinline__ void attn_finish_row(const AttnParams& p, T* out, size_t at, const float* o, int pos, float gmul, int tid,
+                                                int nthreads) {
+  if (p.vcos == nullptr) {
+    for (int c = tid; c < p.Dv; c += nthreads) attn_store<T>(p, out, at + c, o[c] * gmul);
+    return;
+  }
+  pos = pos < 0 ? 0 : (pos >= p.v_max_pos ? p.v_max_pos - 1 : pos);
+  const int half = p.Dv / 2;
+  const float* ct = p.vcos + (size_t)pos * half;
+  const float* st = p.vsin + (size_t)pos * half;
+  for (int i = tid; i < half; i += nthreads) {
+    const int c0 = p.v_layout ? i : 2 * i, c1 = p.v_layout ? i + half : 2 * i + 1;
+    const float u = o[c0], v = o[c1];
+    attn_store<T>(p, out, at + c0, (u * ct[i] + v * st[i]) * gmul);           // the turn by -pos
+    attn_store<T>(p, out, at + c1, (v * ct[i] - u * st[i]) * gmul);
+  }
 }
 
 constexpr int AT_MAXV = 16;         // value columns per lane: Dv <= 512
@@ -299,7 +372,7 @@ __global__ void __launch_bounds__(AR_WARPS * 32) attn_rows_kernel(AttnParams p, 
   const int base = p.cache_len ? *p.cache_len : 0;
   const int lo = p.pad_left ? p.pad_left[b] : 0;
   const int hi_cta = base + min(q0 + AR_QB, p.S) - 1;    // last key any query of this CTA sees
-  const int lo_cta = p.window > 0 ? max(lo, base + q0 - p.window + 1) : lo;      // first key any query of this CTA sees
+  const int lo_cta = attn_first_visible(p, lo, base + q0);      // first key any query of this CTA sees (its first query's)
   for (int i = threadIdx.x; i < AR_QB * DP; i += blockDim.x) {
     const int r = i / DP, c = i % DP, s = q0 + r;
     Qs[i] = (s < p.S && c < p.D) ? to_f(q[((size_t)(b * p.S + s) * p.H + h) * p.D + c]) : 0.0f;
@@ -325,7 +398,7 @@ __global__ void __launch_bounds__(AR_WARPS * 32) attn_rows_kernel(AttnParams p, 
     for (int qi = 0; qi < AR_QW; ++qi) {
       const int s = q0 + warp * AR_QW + qi;
       hi_q[qi] = base + s;
-      lo_q[qi] = p.window > 0 ? max(lo, hi_q[qi] - p.window + 1) : lo;
+      lo_q[qi] = attn_first_visible(p, lo, hi_q[qi]);
       on[qi] = s < p.S && j0 <= hi_q[qi] && j0 + 31 >= lo_q[qi];         // warp-uniform
       if (on[qi]) jend = max(jend, min(32, hi_q[qi] - j0 + 1));
     }
@@ -377,12 +450,26 @@ __global__ void __launch_bounds__(AR_WARPS * 32) attn_rows_kernel(AttnParams p, 
       }
     }
   }
+  if (p.vcos) __syncthreads();                             // every warp is done with the last value tile: its rows are reused below
 #pragma unroll
   for (int qi = 0; qi < AR_QW; ++qi) {
     const int s = q0 + warp * AR_QW + qi;
     if (s >= p.S) continue;
     const int m = b * p.S + s;
-    float gmul = attn_inv_denominator(p, mrun[qi], lrun[qi]);  // a padding query sees nothing: its row is zero
+    float gmul = attn_inv_denominator(p, mrun[qi], lrun[qi], h);  // a padding query sees nothing: its row is zero
+    if (p.vcos) {                                          // the normalised sum meets in the warp's row of shared memory first
+      float* orow = Vs + warp * DVP;
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int c = lane + 32 * i;
+        if (c < p.Dv) orow[c] = acc[qi][i] * gmul;
+      }
+      __syncwarp();
+      const float gate = p.gate ? sigmoid_f(p.gate[(size_t)m * p.ldg + h]) : 1.0f;
+      attn_finish_row<T>(p, out, ((size_t)m * p.H + h) * p.Dv, orow, base + s - lo, gate, lane, 32);
+      __syncwarp();
+      continue;
+    }
     if (p.gate) gmul *= sigmoid_f(p.gate[(size_t)m * p.ldg + h]);
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
@@ -410,8 +497,8 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(AttnParams p
   for (int c = threadIdx.x; c < p.D; c += blockDim.x) qs[c] = to_f(qr[c]);
   __syncthreads();
   const int hi = p.cache_len ? *p.cache_len : 0;
-  int lo = p.pad_left ? p.pad_left[b] : 0;
-  if (p.window > 0) lo = max(lo, hi - p.window + 1);
+  const int lo_seq = p.pad_left ? p.pad_left[b] : 0;     // where the row's sequence starts
+  const int lo = attn_first_visible(p, lo_seq, hi);
   const T* kbase = kc + (size_t)b * p.k_bs + (size_t)g * p.k_hs;
   const T* vbase = vc + (size_t)b * p.v_bs + (size_t)g * p.v_hs;
   float mrun = -INFINITY, lrun = 0.0f, acc[AT_MAXV] = {};
@@ -428,7 +515,20 @@ __global__ void __launch_bounds__(AD_WARPS * 32) attn_decode_kernel(AttnParams p
   for (int w = 0; w < AD_WARPS; ++w) mall = fmaxf(mall, ml[2 * w]);
   float lall = 0.0f;
   for (int w = 0; w < AD_WARPS; ++w) if (ml[2 * w] != -INFINITY) lall += ml[2 * w + 1] * expf(ml[2 * w] - mall);
-  float gmul = attn_inv_denominator(p, mall, lall);
+  float gmul = attn_inv_denominator(p, mall, lall, h);
+  if (p.vcos) {                                            // the normalised sum meets in shared memory, then turns back
+    float o[(32 * AT_MAXV + AD_WARPS * 32 - 1) / (AD_WARPS * 32)];
+    for (int c = threadIdx.x, i = 0; c < p.Dv; c += blockDim.x, ++i) {
+      o[i] = 0.0f;
+      for (int w = 0; w < AD_WARPS; ++w) if (ml[2 * w] != -INFINITY) o[i] += part[w * p.Dv + c] * expf(ml[2 * w] - mall);
+    }
+    __syncthreads();
+    for (int c = threadIdx.x, i = 0; c < p.Dv; c += blockDim.x, ++i) part[c] = o[i] * gmul;
+    __syncthreads();
+    const float gate = p.gate ? sigmoid_f(p.gate[(size_t)b * p.ldg + h]) : 1.0f;
+    attn_finish_row<T>(p, out, ((size_t)b * p.H + h) * p.Dv, part, hi - lo_seq, gate, threadIdx.x, blockDim.x);
+    return;
+  }
   if (p.gate) gmul *= sigmoid_f(p.gate[(size_t)b * p.ldg + h]);
   for (int c = threadIdx.x; c < p.Dv; c += blockDim.x) {
     float o = 0.0f;
@@ -466,8 +566,8 @@ __global__ void __launch_bounds__(AS_WARPS * 32) attn_split_kernel(AttnParams p,
   float* Vs = v_in_k ? Ks : Ks + 32 * DP;                // [32][DVP]
   const int DVP = v_in_k ? DP : (p.Dv + 3) & ~3;
   const int hi = p.cache_len ? *p.cache_len : 0;         // the new token's own slot
-  int lo = p.pad_left ? p.pad_left[b] : 0;
-  if (p.window > 0) lo = max(lo, hi - p.window + 1);
+  const int lo_seq = p.pad_left ? p.pad_left[b] : 0;     // where the row's sequence starts
+  const int lo = attn_first_visible(p, lo_seq, hi);
   // the R query rows are consecutive: staged like a key tile (rows beyond R fall into the key buffer, which is filled later)
   stage_rows<T>(Qs, DP, q + ((size_t)b * p.H + (size_t)g * RG + r0) * p.D, p.D, p.D, 0, R - 1);
   float mrun[AS_RW], lrun[AS_RW], acc[AS_RW][NV];
@@ -571,7 +671,21 @@ __global__ void attn_merge_kernel(AttnParams p, const float* __restrict__ part, 
   }
   __syncthreads();
   const float lall = tot;
-  float gmul = attn_inv_denominator(p, top, lall);
+  float gmul = attn_inv_denominator(p, top, lall, h);
+  if (p.vcos) {                                            // the normalised sum meets in shared memory, then turns back
+    __shared__ float orow[32 * AT_MAXV];
+    for (int c = threadIdx.x; c < p.Dv; c += blockDim.x) {
+      float o = 0.0f;
+#pragma unroll 8
+      for (int zz = 0; zz < splits; ++zz) o = fmaf(src[(size_t)zz * (p.Dv + 2) + 2 + c], wz[zz], o);
+      orow[c] = o * gmul;
+    }
+    __syncthreads();
+    const float gate = p.gate ? sigmoid_f(p.gate[(size_t)b * p.ldg + h]) : 1.0f;
+    const int hi = p.cache_len ? *p.cache_len : 0;
+    attn_finish_row<T>(p, out, ((size_t)b * p.H + h) * p.Dv, orow, hi - (p.pad_left ? p.pad_left[b] : 0), gate, threadIdx.x, blockDim.x);
+    return;
+  }
   if (p.gate) gmul *= sigmoid_f(p.gate[(size_t)b * p.ldg + h]);
   for (int c = threadIdx.x; c < p.Dv; c += blockDim.x) {
     float o = 0.0f;
@@ -597,22 +711,45 @@ __global__ void head_gate_kernel(T* __restrict__ out, const float* __restrict__ 
 
 using namespace jl;
 
-extern "C" JL_API int jl_attn_prep(const float* y, int ldy, int q_off, int k_off, int v_off, void* q_out, void* k_cache,
-                                   void* v_cache, const float* cos_t, const float* sin_t, int max_pos, int rot, int unit_norm,
-                                   float eps, const int* cache_len, const int* pad_left, int B, int S, int H, int G, int D, int Dv,
-                                   int T_cap, const float* bias, int v_norm, int v_token_major, int dtype, void* stream) {
-  JL_CHECK_ARG(B >= 1 && S >= 1 && H >= 1 && G >= 1 && D >= 1 && Dv >= 1, "jl_attn_prep: bad shape");
-  JL_CHECK_ARG(rot >= 0 && rot <= D && rot % 2 == 0, "jl_attn_prep: rot=%d must be even and <= D=%d", rot, D);
-  JL_CHECK_ARG(k_off >= 0 || (k_cache == nullptr && v_cache == nullptr), "jl_attn_prep: queries-only call takes no caches");
-  PrepParams p{y, ldy, q_off, k_off, v_off, B, S, H, G, D, Dv, T_cap, rot, cos_t, sin_t, max_pos, unit_norm, eps, cache_len, pad_left,
-               bias, v_norm, v_token_major};
-  const int n_heads = k_off >= 0 ? H + 2 * G : H;
-  const int pair_loads = D % 2 == 0 && ldy % 2 == 0 && q_off % 2 == 0 && (k_off < 0 || k_off % 2 == 0) && (uintptr_t)y % 8 == 0;
-  dim3 grid(B * S, (n_heads + AP_WARPS - 1) / AP_WARPS);
+static int attn_prep_launch(PrepParams p, void* q_out, void* k_cache, void* v_cache, int dtype, void* stream) {
+  JL_CHECK_ARG(p.B >= 1 && p.S >= 1 && p.H >= 1 && p.G >= 1 && p.D >= 1 && p.Dv >= 1, "jl_attn_prep: bad shape");
+  JL_CHECK_ARG(p.rot >= 0 && p.rot <= p.D && p.rot % 2 == 0, "jl_attn_prep: rot=%d must be even and <= D=%d", p.rot, p.D);
+  JL_CHECK_ARG(p.k_off >= 0 || (k_cache == nullptr && v_cache == nullptr), "jl_attn_prep: queries-only call takes no caches");
+  JL_CHECK_ARG(p.layout == 0 || p.layout == 1, "jl_attn_prep: layout %d", p.layout);
+  JL_CHECK_ARG((p.qw == nullptr) == (p.kw == nullptr), "jl_attn_prep: the q and k norm weights come together");
+  JL_CHECK_ARG(!(p.unit_norm && (p.qw != nullptr || p.layout != 0)),
+               "jl_attn_prep: unit-RMS scaling after the rotation goes with interleaved pairs and no weighted norm");
+  JL_CHECK_ARG(p.vcos == nullptr || (p.vsin != nullptr && p.Dv % 2 == 0 && p.v_max_pos >= 1 && !p.v_token_major),
+               "jl_attn_prep: rotated values need an even Dv=%d and head-major caches", p.Dv);
+  const int n_heads = p.k_off >= 0 ? p.H + 2 * p.G : p.H;
+  const int pair_loads = p.D % 2 == 0 && p.ldy % 2 == 0 && p.q_off % 2 == 0 && (p.k_off < 0 || p.k_off % 2 == 0) && (uintptr_t)p.y % 8 == 0;
+  dim3 grid(p.B * p.S, (n_heads + AP_WARPS - 1) / AP_WARPS);
   JL_DISPATCH_DTYPE(dtype, JL_LAUNCH_PDL(attn_prep_kernel<T>, dim3(grid), dim3(AP_WARPS * 32), 0, (cudaStream_t)stream, p, (T*)q_out, (T*)k_cache,
                                                                                                 (T*)v_cache, n_heads, pair_loads));
   JL_CUDA(cudaGetLastError());
   return JL_OK;
+}
+
+extern "C" JL_API int jl_attn_prep(const float* y, int ldy, int q_off, int k_off, int v_off, void* q_out, void* k_cache,
+                                   void* v_cache, const float* cos_t, const float* sin_t, int max_pos, int rot, int unit_norm,
+                                   float eps, const int* cache_len, const int* pad_left, int B, int S, int H, int G, int D, int Dv,
+                                   int T_cap, const float* bias, int v_norm, int v_token_major, int dtype, void* stream) {
+  PrepParams p{y, ldy, q_off, k_off, v_off, B, S, H, G, D, Dv, T_cap, rot, cos_t, sin_t, max_pos, unit_norm, eps, cache_len, pad_left,
+               bias, v_norm, v_token_major, 0, nullptr, nullptr, nullptr, nullptr, 0, 0};
+  return attn_prep_launch(p, q_out, k_cache, v_cache, dtype, stream);
+}
+
+// The same with the newer pieces: `layout` of the rotated q / k pairs, an RMS norm with weights q_norm_w / k_norm_w [D] before the
+// rotation, and values rotated at their own position with the tables v_cos / v_sin [v_max_pos][Dv/2] (pairs as v_layout).
+extern "C" JL_API int jl_attn_prep_ex(const float* y, int ldy, int q_off, int k_off, int v_off, void* q_out, void* k_cache,
+                                      void* v_cache, const float* cos_t, const float* sin_t, int max_pos, int rot, int layout,
+                                      int unit_norm, const void* q_norm_w, const void* k_norm_w, float eps, const float* v_cos,
+                                      const float* v_sin, int v_max_pos, int v_layout, const int* cache_len, const int* pad_left,
+                                      int B, int S, int H, int G, int D, int Dv, int T_cap, const float* bias, int v_norm,
+                                      int v_token_major, int dtype, void* stream) {
+  PrepParams p{y, ldy, q_off, k_off, v_off, B, S, H, G, D, Dv, T_cap, rot, cos_t, sin_t, max_pos, unit_norm, eps, cache_len, pad_left,
+               bias, v_norm, v_token_major, layout, q_norm_w, k_norm_w, v_cos, v_sin, v_max_pos, v_layout};
+  return attn_prep_launch(p, q_out, k_cache, v_cache, dtype, stream);
 }
 
 extern "C" JL_API int jl_attn_generic_splits(int B, int H, int G, int T_cap) {
@@ -629,13 +766,18 @@ static int attn_launch(const void* q, const void* k_cache, const void* v_cache, 
                        const int* cache_len, const int* pad_left, int B, int S, int H, int G, int D, int Dv, int T_cap, int ldk,
                        int ldv, int window, float scale, float* scratch, int splits, int dtype, void* stream,
                        long long k_bs = 0, long long k_hs = 0, long long v_bs = 0, long long v_hs = 0, int sink = 0,
-                       float* out32 = nullptr) {
+                       float* out32 = nullptr, int chunk = 0, const float* sink_logit = nullptr, const float* vcos = nullptr,
+                       const float* vsin = nullptr, int v_max_pos = 0, int v_layout = 0) {
   JL_CHECK_ARG(B >= 1 && S >= 1 && G >= 1 && H % G == 0, "jl_attn_generic: H=%d not a multiple of G=%d", H, G);
   JL_CHECK_ARG(Dv <= 32 * AT_MAXV, "jl_attn_generic: value size %d above %d", Dv, 32 * AT_MAXV);
   JL_CHECK_ARG(ldk >= D && ldv >= Dv && window >= 0, "jl_attn_generic: bad pitch %d / %d or window %d", ldk, ldv, window);
   if (k_bs == 0 && k_hs == 0) { k_hs = (long long)T_cap * ldk; k_bs = k_hs * G; }
   if (v_bs == 0 && v_hs == 0) { v_hs = (long long)T_cap * ldv; v_bs = v_hs * G; }
-  AttnParams p{B, S, H, G, D, Dv, T_cap, ldk, ldv, k_bs, k_hs, v_bs, v_hs, window, scale, cache_len, pad_left, gate, ldg, sink, out32};
+  JL_CHECK_ARG(chunk >= 0 && (sink_logit == nullptr || sink), "jl_attn_generic: chunk %d, a sink logit without a sink", chunk);
+  JL_CHECK_ARG(vcos == nullptr || (vsin != nullptr && Dv % 2 == 0 && v_max_pos >= 1 && (v_layout == 0 || v_layout == 1)),
+               "jl_attn_generic: rotated values need both tables and an even Dv=%d", Dv);
+  AttnParams p{B, S, H, G, D, Dv, T_cap, ldk, ldv, k_bs, k_hs, v_bs, v_hs, window, scale, cache_len, pad_left, gate, ldg, sink, out32,
+               chunk, sink_logit, vcos, vsin, v_max_pos, v_layout};
   cudaStream_t st = (cudaStream_t)stream;
   if (S == 1 && scratch != nullptr && splits >= 1 && splits <= 64) {
     const int dp = ((D + 3) & ~3) + 4;
@@ -691,6 +833,20 @@ extern "C" JL_API int jl_attn_windowed(const void* q, const void* k_cache, const
   JL_CHECK_ARG(out != nullptr || out32 != nullptr, "jl_attn_windowed: no output");
   return attn_launch(q, k_cache, v_cache, out, nullptr, 0, cache_len, pad_left, B, S, H, G, D, Dv, T_cap, ldk, ldv, window, scale,
                      scratch, splits, dtype, stream, k_bs, k_hs, v_bs, v_hs, sink, out32);
+}
+
+// Everything the attention kernels take: gate (fp32 pre-activation, column h of row m, pitch ldg), window, blocks of `chunk`
+// positions, a sink (score 0, or sink_logit[h]), values cached rotated (v_cos / v_sin [v_max_pos][Dv/2], pairs as v_layout).
+extern "C" JL_API int jl_attn_masked(const void* q, const void* k_cache, const void* v_cache, void* out, const float* gate, int ldg,
+                                     const int* cache_len, const int* pad_left, int B, int S, int H, int G, int D, int Dv, int T_cap,
+                                     int ldk, int ldv, long long k_bs, long long k_hs, long long v_bs, long long v_hs, int window,
+                                     int chunk, float scale, float* scratch, int splits, int sink, const float* sink_logit,
+                                     const float* v_cos, const float* v_sin, int v_max_pos, int v_layout, float* out32, int dtype,
+                                     void* stream) {
+  JL_CHECK_ARG(out != nullptr || out32 != nullptr, "jl_attn_masked: no output");
+  return attn_launch(q, k_cache, v_cache, out, gate, ldg, cache_len, pad_left, B, S, H, G, D, Dv, T_cap, ldk, ldv, window, scale,
+                     scratch, splits, dtype, stream, k_bs, k_hs, v_bs, v_hs, sink, out32, chunk, sink_logit, v_cos, v_sin, v_max_pos,
+                     v_layout);
 }
 
 extern "C" JL_API int jl_latent_prep(const float* y, int ldy, int q_off, int q_rank, int kv_off, int kv_rank, int rot_dim, int rot,

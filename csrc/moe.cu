@@ -1,9 +1,11 @@
 // Mixture-of-experts routing for the hybrid decoder family: choosing experts per token, ordering the (token, choice) pairs
 // by expert for the grouped linear kernels (seq_linear.cu), and the weighted sum of the experts' outputs.
 //
-//   route    one warp per token: scores (sigmoid or softmax of the fp32 router logits), optional restriction to the best
-//            groups of neighbouring experts, the `top` largest of what is left, weights = chosen scores over their sum
-//            (when normalised) times a constant.  Everything in fp32.
+//   route    one warp per token: scores (sigmoid or softmax of the fp32 router logits), choice scores (scores plus an optional
+//            per-expert bias that only the choice sees), optional restriction to the best groups of neighbouring experts, the
+//            `top` largest choice scores of what is left, weights = chosen scores over their sum (when normalised) times a
+//            constant.  The last E - n_real router outputs can be identity experts (no matrices: their output is the input):
+//            a chosen one is reported as expert -1 and its weight is summed per token.  Everything in fp32.
 //   sort     one CTA: counts per expert, segments rounded up to whole row tiles, the sorted position of every pair, the
 //            source token of every sorted row and the expert of every tile.
 //   combine  y[m, :] = sum_k weight[m, k] * z[pos[m, k], :]  (+ sigmoid(gate logit[m]) * shared[m, :]).
@@ -24,6 +26,9 @@ struct RouteParams {
   float scale;
   int* idx; float* wt;              // [M][top]
   const float* bias;                // [E] fp32 added to the logits, or nullptr
+  const float* choice_bias;         // [E] fp32 added to the scores for the choice (groups and top) only, or nullptr
+  int n_real;                       // experts 0 .. n_real-1 have matrices; n_real .. E-1 are identity experts
+  float* ident_w;                   // [M]: sum of the weights of the identity experts a token chose (n_real < E)
 };
 
 constexpr int RT_WARPS = 4;
@@ -62,7 +67,8 @@ __global__ void __launch_bounds__(RT_WARPS * 32) moe_route_kernel(RouteParams p)
     for (int e = lane; e < p.E; e += 32) s[e] = sigmoid_f(logit(e));
   }
   __syncwarp();
-  for (int e = lane; e < p.E; e += 32) work[e] = s[e];
+  for (int e = lane; e < p.E; e += 32) work[e] = p.choice_bias ? s[e] + p.choice_bias[e] : s[e];
+  __syncwarp();
   if (ng) {
     const int per = p.E / ng;
     for (int g = lane; g < ng; g += 32) {                        // sum of the group's group_top largest scores
@@ -71,7 +77,7 @@ __global__ void __launch_bounds__(RT_WARPS * 32) moe_route_kernel(RouteParams p)
       for (int t = 0; t < p.group_top && t < per; ++t) {         // t-th largest: the largest that comes after (last, last_i)
         float best = -INFINITY; int bi = -1;
         for (int j = 0; j < per; ++j) {
-          const float v = s[g * per + j];
+          const float v = work[g * per + j];
           const bool after = v < last || (v == last && j > last_i);
           if (after && (v > best || bi < 0)) { best = v; bi = j; }
         }
@@ -91,10 +97,10 @@ __global__ void __launch_bounds__(RT_WARPS * 32) moe_route_kernel(RouteParams p)
       __syncwarp();
     }
     for (int e = lane; e < p.E; e += 32)
-      if (gs[e / per] != -INFINITY) work[e] = -1.0f;               // experts outside the kept groups cannot be chosen
+      if (gs[e / per] != -INFINITY) work[e] = -INFINITY;           // experts outside the kept groups cannot be chosen
   }
   __syncwarp();
-  float sum = 0.0f, mine = 0.0f; int mine_i = 0;
+  float sum = 0.0f, mine = 0.0f, ident = 0.0f; int mine_i = 0;
   for (int t = 0; t < p.top; ++t) {
     float v = -INFINITY; int ei = 0x7fffffff;
     for (int e = lane; e < p.E; e += 32)
@@ -103,16 +109,19 @@ __global__ void __launch_bounds__(RT_WARPS * 32) moe_route_kernel(RouteParams p)
     if (ei == 0x7fffffff) ei = 0;
     const float sc = s[ei];
     sum += sc;
-    if (lane == t % 32 && t < 32) { mine = sc; mine_i = ei; }
-    if (t >= 32 && lane == 0) { p.idx[(size_t)m * p.top + t] = ei; p.wt[(size_t)m * p.top + t] = sc; }    // weights scaled below
+    const int eo = ei < p.n_real ? ei : -1;                      // an identity expert has no matrices to run
+    if (eo < 0) ident += sc;
+    if (lane == t % 32 && t < 32) { mine = sc; mine_i = eo; }
+    if (t >= 32 && lane == 0) { p.idx[(size_t)m * p.top + t] = eo; p.wt[(size_t)m * p.top + t] = sc; }    // weights scaled below
     __syncwarp();
-    if (lane == 0) work[ei] = -2.0f;
+    if (lane == 0) work[ei] = -INFINITY;
     __syncwarp();
   }
   const float mul = (p.normalise ? 1.0f / (sum + 1e-20f) : 1.0f) * p.scale;
   if (lane < p.top) { p.idx[(size_t)m * p.top + lane] = mine_i; p.wt[(size_t)m * p.top + lane] = mine * mul; }
   if (p.top > 32 && lane == 0)
     for (int t = 32; t < p.top; ++t) p.wt[(size_t)m * p.top + t] *= mul;
+  if (p.ident_w && lane == 0) p.ident_w[m] = ident * mul;
 }
 
 // One CTA orders the n = M * top pairs by expert.  counts / offsets live in shared memory (E + 1 ints each).
@@ -128,7 +137,8 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ 
   for (int i = threadIdx.x; i < cap; i += blockDim.x) row_src[i] = -1;
   for (int i = threadIdx.x; i < cap / tile; i += blockDim.x) tile_group[i] = -1;
   __syncthreads();
-  for (int i = threadIdx.x; i < n; i += blockDim.x) pos[i] = atomicAdd(&count[idx[i]], 1);       // rank within its expert
+  for (int i = threadIdx.x; i < n; i += blockDim.x)               // rank within its expert (expert < 0: a pair that runs no expert)
+    pos[i] = idx[i] >= 0 ? atomicAdd(&count[idx[i]], 1) : -1;
   __syncthreads();
   if (threadIdx.x == 0) {
     int at = 0;
@@ -140,16 +150,19 @@ __global__ void __launch_bounds__(1024) moe_sort_kernel(const int* __restrict__ 
   for (int e = threadIdx.x; e < E; e += blockDim.x)
     for (int t = start[e] / tile; t < start[e + 1] / tile; ++t) tile_group[t] = e;
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    if (idx[i] < 0) continue;                                      // pos stays -1: the combine pass skips the pair
     const int at = start[idx[i]] + pos[i];
     pos[i] = at;
     row_src[at] = i / top;
   }
 }
 
+template <typename T>
 __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restrict__ z, int ldz, const int* __restrict__ pos,
                                                           const float* __restrict__ wt, int top, const float* __restrict__ shared,
                                                           int lds, const float* __restrict__ gate, int ldg,
-                                                          float* __restrict__ out, int W) {
+                                                          float* __restrict__ out, int W, const int* __restrict__ idx,
+                                                          const float* __restrict__ ident_w, const T* __restrict__ x, int ldx) {
   pdl_wait();                      // programmatic dependent launch: nothing is read before the predecessor is done
   pdl_launch_dependents();
   const size_t m = blockIdx.x;
@@ -157,9 +170,11 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restric
   for (int i = threadIdx.x; i < W; i += blockDim.x) {
     float acc = 0.0f;
     for (int k = 0; k < top; ++k) {
+      if (idx && idx[m * top + k] < 0) continue;                   // an identity expert: its share comes with ident_w below
       const size_t r = pos ? (size_t)pos[m * top + k] : m * top + k;
       acc = fmaf(wt[m * top + k], z[r * ldz + i], acc);
     }
+    if (ident_w) acc = fmaf(ident_w[m], to_f(x[m * ldx + i]), acc);
     if (shared) acc = fmaf(g, shared[m * lds + i], acc);
     out[m * W + i] = acc;
   }
@@ -187,19 +202,35 @@ __global__ void __launch_bounds__(128) moe_gather_kernel(const T* __restrict__ x
 
 using namespace jl;
 
-extern "C" JL_API int jl_moe_route(const float* z, int ldz, int M, int E, int top, int groups, int keep, int group_top, int score,
-                                   int normalise, float scale, const float* bias, int* idx, float* wt, void* stream) {
+static int moe_route_launch(const float* z, int ldz, int M, int E, int top, int groups, int keep, int group_top, int score,
+                            int normalise, float scale, const float* bias, const float* choice_bias, int n_real, float* ident_w,
+                            int* idx, float* wt, void* stream) {
   JL_CHECK_ARG(M >= 1 && E >= 1 && top >= 1 && top <= E && ldz >= E, "jl_moe_route: bad shape M=%d E=%d top=%d ldz=%d", M, E, top, ldz);
   JL_CHECK_ARG(groups <= 1 || (E % groups == 0 && keep >= 1 && keep <= groups && group_top >= 1 && keep * (E / groups) >= top),
                "jl_moe_route: %d groups of %d experts, keep %d, cannot give %d choices", groups, groups > 0 ? E / groups : 0, keep, top);
   JL_CHECK_ARG(score == SCORE_SIGMOID || score == SCORE_SOFTMAX, "jl_moe_route: score function %d", score);
-  RouteParams p{z, ldz, M, E, top, groups, keep, group_top, score, normalise, scale, idx, wt, bias};
+  JL_CHECK_ARG(n_real >= 1 && n_real <= E && (n_real == E || ident_w != nullptr), "jl_moe_route: %d of %d experts with matrices", n_real, E);
+  RouteParams p{z, ldz, M, E, top, groups, keep, group_top, score, normalise, scale, idx, wt, bias, choice_bias, n_real, ident_w};
   const size_t smem = (size_t)RT_WARPS * (2 * E + (groups > 1 ? groups : 0)) * sizeof(float);
   JL_CHECK_ARG(smem <= 200 * 1024, "jl_moe_route: %d experts do not fit shared memory", E);
   if (smem > 48 * 1024) JL_CUDA(cudaFuncSetAttribute(moe_route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   JL_LAUNCH_PDL(moe_route_kernel, dim3((M + RT_WARPS - 1) / RT_WARPS), dim3(RT_WARPS * 32), smem, stream, p);
   JL_CUDA(cudaGetLastError());
   return JL_OK;
+}
+
+extern "C" JL_API int jl_moe_route(const float* z, int ldz, int M, int E, int top, int groups, int keep, int group_top, int score,
+                                   int normalise, float scale, const float* bias, int* idx, float* wt, void* stream) {
+  return moe_route_launch(z, ldz, M, E, top, groups, keep, group_top, score, normalise, scale, bias, nullptr, E, nullptr, idx, wt, stream);
+}
+
+// The same with a choice bias (added to the scores for groups and top only) and identity experts: router outputs n_real .. E-1
+// have no matrices; a chosen one is reported as expert -1 and its weight is added to ident_w[m].
+extern "C" JL_API int jl_moe_route_ex(const float* z, int ldz, int M, int E, int top, int groups, int keep, int group_top, int score,
+                                      int normalise, float scale, const float* bias, const float* choice_bias, int n_real,
+                                      float* ident_w, int* idx, float* wt, void* stream) {
+  return moe_route_launch(z, ldz, M, E, top, groups, keep, group_top, score, normalise, scale, bias, choice_bias, n_real, ident_w, idx,
+                          wt, stream);
 }
 
 // Rows of the sorted layout for n pairs over E experts with row tiles of `tile`: every expert's segment is rounded up.
@@ -219,7 +250,21 @@ extern "C" JL_API int jl_moe_sort(const int* idx, int M, int top, int E, int til
 extern "C" JL_API int jl_moe_combine(const float* z, int ldz, const int* pos, const float* wt, int top, const float* shared, int lds,
                                      const float* gate, int ldg, float* out, int M, int W, void* stream) {
   JL_CHECK_ARG(M >= 1 && W >= 1 && top >= 1 && ldz >= W, "jl_moe_combine: bad shape");
-  JL_LAUNCH_PDL(moe_combine_kernel, dim3(M), dim3(256), 0, stream, z, ldz, pos, wt, top, shared, lds, gate, ldg, out, W);
+  JL_LAUNCH_PDL(moe_combine_kernel<float>, dim3(M), dim3(256), 0, stream, z, ldz, pos, wt, top, shared, lds, gate, ldg, out, W,
+                (const int*)nullptr, (const float*)nullptr, (const float*)nullptr, 0);
+  JL_CUDA(cudaGetLastError());
+  return JL_OK;
+}
+
+// The same for a router with identity experts: pairs with idx < 0 ran no expert (their rows of z are not read); ident_w[m] · x[m, :]
+// (x in `dtype`, row pitch ldx) is added instead.
+extern "C" JL_API int jl_moe_combine_ex(const float* z, int ldz, const int* pos, const float* wt, int top, const float* shared, int lds,
+                                        const float* gate, int ldg, float* out, int M, int W, const int* idx, const float* ident_w,
+                                        const void* x, int ldx, int dtype, void* stream) {
+  JL_CHECK_ARG(M >= 1 && W >= 1 && top >= 1 && ldz >= W, "jl_moe_combine: bad shape");
+  JL_CHECK_ARG(ident_w == nullptr || (x != nullptr && ldx >= W), "jl_moe_combine: identity weights without the input rows");
+  JL_DISPATCH_DTYPE(dtype, JL_LAUNCH_PDL(moe_combine_kernel<T>, dim3(M), dim3(256), 0, stream, z, ldz, pos, wt, top, shared, lds, gate,
+                                         ldg, out, W, idx, ident_w, (const T*)x, ldx));
   JL_CUDA(cudaGetLastError());
   return JL_OK;
 }

@@ -14,7 +14,7 @@
 namespace jl {
 
 // Many small products in one launch.  Plain batches: batch z reads x + (z / x_div) * x_bs, weights
-// w + (w_index ? w_index[z] : z) * w_bs and writes out + z * o_bs (per-head matrices; one expert per (token, choice) pair when
+// w + (w_index ? w_index[z] : z) * w_bs (w_index[z] < 0: the batch is skipped) and writes out + z * o_bs (per-head matrices; one expert per (token, choice) pair when
 // decoding a mixture of experts: x_div = choices per token, so that the pairs of a token read the same input row).
 // Sorted rows (tiled kernel only): the rows come in tiles of LT_BM that each belong to one weight matrix, tile_group[tile]
 // (< 0: empty tile); row position p reads input row row_src[p] (< 0: padding, read as zero; nullptr: p itself) and writes
@@ -54,6 +54,7 @@ __global__ void __launch_bounds__(LR_WARPS * 32) linear_rows_kernel(const T* __r
   pdl_wait();                      // programmatic dependent launch: nothing is read before the predecessor is done
   pdl_launch_dependents();
   __shared__ float red[LR_WARPS][LR_ROWS][M];
+  if (g.w_index && g.w_index[blockIdx.y] < 0) return;            // a batch without a matrix (uniform for the CTA): nothing is written
   {
     const long long z = blockIdx.y;
     x += (z / g.x_div) * g.x_bs;
@@ -133,6 +134,7 @@ __global__ void __launch_bounds__(256) linear_tiled_kernel(const T* __restrict__
     w += (long long)e * g.w_bs;
   } else {
     const long long z = blockIdx.z;
+    if (g.w_index && g.w_index[z] < 0) return;                     // a batch without a matrix (uniform for the CTA)
     x += (z / g.x_div) * g.x_bs;
     w += (g.w_index ? (long long)g.w_index[z] : z) * g.w_bs;
     out += z * g.o_bs;
@@ -206,7 +208,7 @@ extern "C" JL_API int jl_linear_any(const void* x, int ldx, const void* w, void*
                                     float p0, float p1, int dtype, int out_f32, void* stream) {
   JL_CHECK_ARG(M >= 1 && N >= 1 && K >= 1 && ldx >= K && ldo >= N, "jl_linear_any: bad shape M=%d N=%d K=%d ldx=%d ldo=%d", M, N,
                K, ldx, ldo);
-  JL_CHECK_ARG(act >= 0 && act <= ACT_SIGMOID, "jl_linear_any: bad activation %d", act);
+  JL_CHECK_ARG(act >= 0 && act <= ACT_LAST, "jl_linear_any: bad activation %d", act);
   cudaStream_t st = (cudaStream_t)stream;
   int rc;
   if (dtype == DT_BF16)
@@ -226,7 +228,7 @@ extern "C" JL_API int jl_linear_grouped(const void* x, int ldx, long long x_bs, 
                                         void* stream) {
   JL_CHECK_ARG(M >= 1 && N >= 1 && K >= 1 && ldx >= K && ldo >= N && nbatch >= 1 && x_div >= 1, "jl_linear_grouped: bad shape M=%d N=%d K=%d ldx=%d ldo=%d",
                M, N, K, ldx, ldo);
-  JL_CHECK_ARG(act >= 0 && act <= ACT_SIGMOID, "jl_linear_grouped: bad activation %d", act);
+  JL_CHECK_ARG(act >= 0 && act <= ACT_LAST, "jl_linear_grouped: bad activation %d", act);
   JL_CHECK_ARG(tile_group == nullptr || M % LT_BM == 0, "jl_linear_grouped: sorted rows come in tiles of %d, M=%d", LT_BM, M);
   JL_CHECK_ARG(nbatch <= 65535, "jl_linear_grouped: %d batches above the grid limit", nbatch);
   cudaStream_t st = (cudaStream_t)stream;

@@ -11,7 +11,8 @@ namespace jl {
 
 enum { DT_BF16 = 0, DT_F32 = 1 };
 // epilogue / activation codes shared by the generic linears and jl_act_cast
-enum { ACT_NONE = 0, ACT_RELU2 = 1, ACT_GELU_TANH = 2, ACT_SILU = 3, ACT_SCALE_SOFTCAP = 4, ACT_SIGMOID = 5 };
+// ACT_XIELU: z > 0: p0 z^2 + z/2;  z <= 0: p1 (e^z - 1 - z) + z/2  (p0, p1 positive, formed by the caller from the layer's two numbers)
+enum { ACT_NONE = 0, ACT_RELU2 = 1, ACT_GELU_TANH = 2, ACT_SILU = 3, ACT_SCALE_SOFTCAP = 4, ACT_SIGMOID = 5, ACT_XIELU = 6, ACT_LAST = ACT_XIELU };
 
 __device__ __forceinline__ float to_f(float v) { return v; }
 __device__ __forceinline__ float to_f(__nv_bfloat16 v) { return __bfloat162float(v); }
@@ -27,6 +28,7 @@ __device__ __forceinline__ float apply_act(float z, int act, float p0, float p1)
     case ACT_GELU_TANH: return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
     case ACT_SILU: return z * sigmoid_f(z);
     case ACT_SIGMOID: return sigmoid_f(z);
+    case ACT_XIELU: return z > 0.0f ? fmaf(p0 * z, z, 0.5f * z) : fmaf(p1, expm1f(z) - z, 0.5f * z);
     case ACT_SCALE_SOFTCAP: { float s = z * p0; return p1 > 0.0f ? p1 * tanhf(s / p1) : s; }
     default: return z;
   }

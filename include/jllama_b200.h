@@ -422,6 +422,49 @@ int jl_delta_scan(const float* u, int ldu, int q_off, int k_off, int v_off, int 
                   const void* a2, const void* a_bias, const void* a_log, float* state, float* o, const int* cache_len,
                   const int* pad_left, int B, int S, int H, int D, int Dv, int R, float* ws, int dtype, void* stream);
 
+/* ---- Pieces added with the looped chunked-attention design (Datozen): learned positions, a per-layer token input, attention
+ * with a weighted q / k norm before the rotation, rotated values, blocks of positions and a learned sink, a router with a
+ * choice bias and identity experts. */
+
+/* out[m] = table[ids[m]] + pos_table[position of m] (fp32 [B*S, W]); token (b, s) is at position *cache_len + s - pad_left[b]
+ * (clamped to P - 1; a negative position is padding and gives a zero row). */
+int jl_embed_pos(const int* ids, const void* table, const void* pos_table, float* out, const int* cache_len, const int* pad_left,
+                 int B, int S, int W, int V, int P, int dtype, void* stream);
+/* out[m, c] = gelu_tanh(t[m, c]) * side[ids[m], col0 + c], c < n; t fp32 (row pitch ldt), side and out of dtype (pitches lds, ldo). */
+int jl_side_gate(const float* t, int ldt, const int* ids, const void* side, int lds, int col0, void* out, int ldo, int M, int n,
+                 int V, int dtype, void* stream);
+/* The per-layer token input for a few rows in one launch: y = w_proj (gelu_tanh(w_gate x) * side[ids[m], col0 .. col0 + n));
+ * x[m] += y / rms(y) * w_side;  if w_next: h[m] = x[m] / rms(x[m]) * w_next.  x fp32 [M, W]; w_gate [n, W], w_proj [W, n]. */
+int jl_token_side(float* x, const int* ids, const void* side, int lds, int col0, const void* w_gate, const void* w_proj,
+                  const void* w_side, const void* w_next, void* h, int M, int W, int n, int V, float eps, int dtype, void* stream);
+/* jl_attn_prep with: `layout` of the rotated q / k pairs (0: (2i, 2i+1), 1: (i, i + rot/2)); q_norm_w / k_norm_w [D] of dtype, an RMS
+ * norm of every head before the rotation (NULL: none); v_cos / v_sin fp32 [v_max_pos][Dv/2]: values rotated at their own position
+ * over all Dv channels before they are cached, pairs as v_layout (NULL: cached as they are). */
+int jl_attn_prep_ex(const float* y, int ldy, int q_off, int k_off, int v_off, void* q_out, void* k_cache, void* v_cache,
+                    const float* cos_t, const float* sin_t, int max_pos, int rot, int layout, int unit_norm, const void* q_norm_w,
+                    const void* k_norm_w, float eps, const float* v_cos, const float* v_sin, int v_max_pos, int v_layout,
+                    const int* cache_len, const int* pad_left, int B, int S, int H, int G, int D, int Dv, int T_cap,
+                    const float* bias, int v_norm, int v_token_major, int dtype, void* stream);
+/* jl_attn_windowed with: gate (fp32 pre-activation of a sigmoid per head, column h of row m, pitch ldg; NULL: none); chunk > 0:
+ * positions form blocks of `chunk` and a query sees the keys of its own block only; sink_logit fp32 [H]: the extra term of the
+ * denominator is exp(sink_logit[h]) (needs sink = 1; NULL: exp(0)); v_cos / v_sin: the cached values were rotated at their own
+ * positions and every head's sum is rotated back by the query's position before the gate. */
+int jl_attn_masked(const void* q, const void* k_cache, const void* v_cache, void* out, const float* gate, int ldg,
+                   const int* cache_len, const int* pad_left, int B, int S, int H, int G, int D, int Dv, int T_cap, int ldk, int ldv,
+                   long long k_bs, long long k_hs, long long v_bs, long long v_hs, int window, int chunk, float scale, float* scratch,
+                   int splits, int sink, const float* sink_logit, const float* v_cos, const float* v_sin, int v_max_pos,
+                   int v_layout, float* out32, int dtype, void* stream);
+/* jl_moe_route with: choice_bias fp32 [E] added to the scores for the choice (group scores and top) only; experts n_real .. E-1
+ * are identity experts: a chosen one is reported as expert -1 (jl_moe_sort and the grouped linears skip it) and its weight is
+ * added to ident_w[m]. */
+int jl_moe_route_ex(const float* z, int ldz, int M, int E, int top, int groups, int keep, int group_top, int score, int normalise,
+                    float scale, const float* bias, const float* choice_bias, int n_real, float* ident_w, int* idx, float* wt,
+                    void* stream);
+/* jl_moe_combine that skips the pairs with idx < 0 and adds ident_w[m] * x[m] (x of dtype, row pitch ldx). */
+int jl_moe_combine_ex(const float* z, int ldz, const int* pos, const float* wt, int top, const float* shared, int lds,
+                      const float* gate, int ldg, float* out, int M, int W, const int* idx, const float* ident_w, const void* x,
+                      int ldx, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

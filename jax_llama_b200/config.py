@@ -293,6 +293,11 @@ class AttentionMixerSpec:
     window: int = 0                 # > 0: a query sees itself and the window - 1 tokens before it
     sink: bool = False              # one more unit in the softmax denominator: a key with score 0 that carries no value
     talking_heads: bool = False     # the heads' weights are mixed by `talk` [heads, heads] after the softmax
+    qk_norm: bool = False           # RMS norm of every q / k head with the weights `q.norm` / `k.norm` [dim] BEFORE the rotation
+    chunk: int = 0                  # > 0: positions form blocks of `chunk`; a query sees the keys of its own block only
+    sink_learned: bool = False      # the sink's logit is `sink` [heads] instead of 0 (needs sink)
+    v_rot: bool = False             # values are rotated at their own position over all vdim channels (frequencies rot.base^(-2m/vdim),
+                                    # the pairing of rot.layout, no interpolation), every head's sum is rotated back at the query's
     kind: str = "attention"
 
 
@@ -385,7 +390,8 @@ class PairEmbeddingSpec:
 
 @dataclass
 class DenseMlpSpec:
-    """down(act(up h)), or with `gated` down(act(gate h) * (up h))."""
+    """down(act(up h)), or with `gated` down(act(gate h) * (up h)).  act "xielu": z > 0: softplus(p) z^2 + z/2, else
+    (1/2 + softplus(q)) (e^z - 1 - z) + z/2, with the layer's own (p, q) in the tensor `act`."""
     ff: int
     act: str = "relu2"
     gated: bool = False
@@ -395,7 +401,7 @@ class DenseMlpSpec:
 @dataclass
 class MoeMlpSpec:
     """Mixture of experts: `experts` feed-forward layers of inner size `ff`, `top` per token.  groups > 1: the experts
-    form equal groups of neighbours, a group scores the sum of its `group_top` largest scores and only the `keep` best
+    form equal groups of neighbours, a group scores the sum of its `group_top` largest choice scores and only the `keep` best
     groups can be chosen.  Weights = chosen scores over their sum, times `scale`.  shared_ff > 0: one more expert runs
     for every token, times a per-token sigmoid gate when shared_gate."""
     experts: int
@@ -414,6 +420,9 @@ class MoeMlpSpec:
     limit: float = 0.0
     shared_limit: float = 0.0
     router_bias: bool = False       # `router.b` is added to the router logits
+    identity: int = 0               # router outputs beyond `experts` that stand for identity experts (output = input, no tensors);
+                                    # groups are formed over experts + identity
+    choice_bias: bool = False       # `correction` [experts + identity] is added to the scores for the choice only (group scores, top)
     kind: str = "moe"
 
 
@@ -443,10 +452,12 @@ class HybridConfig:
     default_eps = 1e-6
     tied_head = False
     embed_norm = False
+    learned_positions = False
 
     def __init__(self, vocab: int, width: int, layers: Any, norm: Optional[Dict[str, Any]] = None,
                  logit_scale: float = 1.0, logit_softcap: Optional[float] = None, residual_mult: float = 1.0,
-                 embedding: Optional[Dict[str, Any]] = None, **extra: Any):
+                 embedding: Optional[Dict[str, Any]] = None, loop: Optional[Dict[str, Any]] = None,
+                 token_side: Optional[Dict[str, Any]] = None, max_positions: Optional[int] = None, **extra: Any):
         self.vocab_size = int(vocab)
         self.hidden_size = int(width)
         self.rms_norm_eps = float((norm or {}).get("eps", self.default_eps))
@@ -456,6 +467,12 @@ class HybridConfig:
         self.embedding_dict = copy.deepcopy(embedding) if embedding else None
         bg = (embedding or {}).get("bigram")
         self.pair_embedding = PairEmbeddingSpec(int(bg["buckets"]), int(bg["mul_prev"]), int(bg["mul_cur"])) if bg else None
+        # layers [start, stop) run `times` times in a row with the same weights (every pass has its own cache and state)
+        self.loop = {k: int(loop[k]) for k in ("start", "stop", "times")} if loop else None
+        # per-layer token input: a second embedding table holds `dim` numbers per layer and token
+        self.token_side_dim = int(token_side["dim"]) if token_side else 0
+        # learned position rows added to the token embedding (designs with `learned_positions`)
+        self.max_positions = int(max_positions) if max_positions else 0
         self.layer_dicts = copy.deepcopy(list(layers))
         self.layers = [HybridLayerSpec(mixer=self._parse_mixer(i, d), mlp=self._parse_mlp(i, d.get("mlp")))
                        for i, d in enumerate(self.layer_dicts)]
@@ -482,9 +499,21 @@ class HybridConfig:
     def num_hidden_layers(self) -> int:
         return len(self.layers)
 
+    def layer_runs(self) -> List[int]:
+        """The layer index of every layer run, in execution order (without a loop: every layer once)."""
+        n = len(self.layers)
+        if not self.loop:
+            return list(range(n))
+        a, b, t = self.loop["start"], self.loop["stop"], self.loop["times"]
+        return list(range(a)) + list(range(a, b)) * t + list(range(b, n))
+
     def validate(self) -> None:
         if self.vocab_size <= 0 or self.hidden_size <= 0 or not self.layers:
             raise ValueError("vocab, width and layers must be non-empty")
+        if self.loop and not (0 <= self.loop["start"] <= self.loop["stop"] <= len(self.layers) and self.loop["times"] >= 1):
+            raise ValueError(f"loop {self.loop} does not fit {len(self.layers)} layers")
+        if self.token_side_dim < 0 or self.max_positions < 0 or (self.learned_positions and self.max_positions <= 0):
+            raise ValueError("token_side.dim and max_positions must be positive where the design has them")
         for i, l in enumerate(self.layers):
             self._validate_layer(i, l)
 
@@ -493,6 +522,12 @@ class HybridConfig:
                              "norm": {"eps": self.rms_norm_eps}, "layers": copy.deepcopy(self.layer_dicts)}
         if self.embedding_dict:
             d["embedding"] = copy.deepcopy(self.embedding_dict)
+        if self.loop:
+            d["loop"] = dict(self.loop)
+        if self.token_side_dim:
+            d["token_side"] = {"dim": self.token_side_dim}
+        if self.max_positions:
+            d["max_positions"] = self.max_positions
         d.update(self._own_keys())
         d.update(self.extra)
         return d
@@ -712,3 +747,72 @@ class BazulornConfig(HybridConfig):
         super().validate()
         if self.pair_embedding is not None and self.pair_embedding.buckets <= 0:
             raise ValueError("embedding.bigram.buckets must be positive")
+
+
+class DatozenConfig(HybridConfig):
+    """Datozen: a decoder of parallel blocks with ONE norm per block — ``x += attention(norm1 x) + ff(norm1 x)`` — followed by a
+    per-layer token input, ``y = proj(gelu(gate x) * Es[token, slice of the layer]); x += norm(y)``.  A stretch of layers can run
+    several times over with the same weights (``loop``), each pass with keys and values of its own.  The token embedding adds a
+    learned position row; the logits are taken against the embedding table.
+
+    Mixer "attention": grouped heads; q and k normed per head with a weight before the rotation; rotary embedding in the
+    half-split pairing with frequency interpolation; values rotated at their own position and the head's sum rotated back at the
+    query's; keys of the query's block of ``mask.size`` positions only; a learned logit per head in the softmax denominator; a
+    sigmoid gate per head.  Feed-forward: dense with the two-parameter "xielu" activation, or a mixture of silu-gated experts
+    with softmax scores over experts and identity experts, a choice bias, groups limited by their best member, unnormalised
+    weights and a shared expert.
+
+    ``config.json``: ``vocab``, ``width``, ``norm.eps``, ``max_positions``, ``token_side.dim``, ``loop.{start, stop, times}`` and
+    ``layers[i]`` = ``{type: "attention", mixer: {heads, kv_heads, dim, vdim, scale, mask.size, rot.{dims, base, scaling.{factor,
+    original, fast, slow}}}, mlp}`` with ``mlp`` null, ``{kind: dense, ff}`` or ``{kind: moe, router.{experts, top, identity,
+    groups.{count, keep}}, expert.ff, shared.ff}``."""
+
+    model_type = "datozen"
+    architecture = "Datozen"
+    block = "parallel_shared"
+    norm_offset = 0.0
+    default_eps = 1e-5
+    tied_head = True
+    embed_norm = False
+    learned_positions = True
+
+    def _parse_mixer(self, i: int, d: Dict[str, Any]) -> Any:
+        m = d["mixer"]
+        kind = d["type"]
+        if kind != "attention":
+            raise ValueError(f"layer {i}: unknown mixer type {kind!r}")
+        rot = RotarySpec.parse(m.get("rot"), "half")
+        return AttentionMixerSpec(
+            heads=int(m["heads"]), kv_heads=int(m.get("kv_heads", m["heads"])), dim=int(m["dim"]), vdim=int(m["vdim"]),
+            scale=float(m["scale"]), rot=rot, kv_from=None, qk_unit_norm=False, head_gate=True, qk_norm=True,
+            chunk=int((m.get("mask") or {}).get("size") or 0), sink=True, sink_learned=True, v_rot=rot is not None)
+
+    def _parse_mlp(self, i: int, mlp: Optional[Dict[str, Any]]) -> Any:
+        if mlp is None:
+            return None
+        kind = mlp.get("kind", "dense")
+        if kind == "dense":
+            return DenseMlpSpec(ff=int(mlp["ff"]), act="xielu", gated=False)
+        if kind == "moe":
+            r = mlp["router"]
+            g = r.get("groups") or {}
+            shared = mlp.get("shared") or {}
+            return MoeMlpSpec(experts=int(r["experts"]), top=int(r["top"]), ff=int(mlp["expert"]["ff"]), act="silu",
+                              score="softmax", groups=int(g.get("count", 1)), keep=int(g.get("keep", g.get("count", 1))),
+                              group_top=1, scale=1.0, normalise=False, shared_ff=int(shared.get("ff", 0)), shared_gate=False,
+                              gated=True, identity=int(r.get("identity", 0)), choice_bias=True)
+        raise ValueError(f"layer {i}: unknown feed-forward kind {kind!r}")
+
+    def _validate_layer(self, i: int, l: HybridLayerSpec) -> None:
+        m = l.mixer
+        if min(m.heads, m.kv_heads, m.dim, m.vdim) <= 0 or m.heads % m.kv_heads or m.chunk < 0:
+            raise ValueError(f"layer {i}: attention sizes heads {m.heads}, kv_heads {m.kv_heads}, block {m.chunk}")
+        if m.rot is not None and (m.rot.dims % 2 or m.rot.dims > m.dim or m.vdim % 2):
+            raise ValueError(f"layer {i}: rot.dims {m.rot.dims} must be even and at most dim {m.dim}, vdim {m.vdim} even")
+        f = l.mlp
+        if f is not None and f.kind == "moe":
+            n = f.experts + f.identity
+            if not 1 <= f.top <= n:
+                raise ValueError(f"layer {i}: top {f.top} of {n} experts")
+            if f.groups > 1 and (n % f.groups or not 1 <= f.keep <= f.groups or f.keep * (n // f.groups) < f.top):
+                raise ValueError(f"layer {i}: {f.groups} groups (keep {f.keep}) cannot give {f.top} of {n} experts")

@@ -7,8 +7,10 @@ Constants (activation, score function, group limits, weight scale, shared expert
 """
 from __future__ import annotations
 
+import math
 from typing import Dict, List, Optional, Tuple
 
+import numpy as np
 import torch
 
 from ..config import DenseMlpSpec, MoeMlpSpec
@@ -26,8 +28,14 @@ def _gated_act(y: torch.Tensor, u_off: int, F: int, act: str, limit: float, dtyp
     return SK.glu_act(y, 0, u_off, F, dtype, kind=SK.GLU_PRODUCT, act=SK.ACTIVATIONS[act], **kw)
 
 
+def _softplus(z: float) -> float:
+    return z if z > 30.0 else math.log1p(math.exp(z))
+
+
 class DenseFeedForward:
-    """down(act(up h)); gated: down(act(gate h) · (up h)) with gate and up stacked into one product."""
+    """down(act(up h)); gated: down(act(gate h) · (up h)) with gate and up stacked into one product.  The "xielu" activation
+    has two numbers (p, q) per layer in the tensor `act`: its coefficients softplus(p) and 1/2 + softplus(q) are formed once,
+    when the weights are loaded."""
 
     kind = "dense"
 
@@ -41,12 +49,20 @@ class DenseFeedForward:
         else:
             self.up = w["up"].contiguous()
         self.down = w["down"].contiguous()
+        self.p0 = self.p1 = 0.0
+        if spec.act == "xielu":
+            if spec.gated:
+                raise ValueError("the xielu activation goes with an ungated layer")
+            p, q = (float(v) for v in w["act"].double().cpu())
+            self.p0, self.p1 = float(np.float32(_softplus(p))), float(np.float32(0.5 + _softplus(q)))
 
     @staticmethod
     def shapes(spec: DenseMlpSpec, W: int) -> Dict[str, Tuple[int, ...]]:
         out = {"up": (spec.ff, W), "down": (W, spec.ff)}
         if spec.gated:
             out["gate"] = (spec.ff, W)
+        if spec.act == "xielu":
+            out["act"] = (2,)
         return out
 
     def weights(self) -> List[torch.Tensor]:
@@ -59,7 +75,7 @@ class DenseFeedForward:
         if self.spec.gated:
             t = _gated_act(SK.linear(h, self.up), self.u_off, self.spec.ff, self.spec.act, 0.0, h.dtype)
         else:
-            t = SK.linear(h, self.up, act=self.act, out_f32=False)
+            t = SK.linear(h, self.up, act=self.act, p0=self.p0, p1=self.p1, out_f32=False)
         return SK.linear(t, self.down)
 
 
@@ -69,7 +85,9 @@ class MoeFeedForward:
     one batched launch each.  Many rows (prompts): the pairs are ordered by expert into whole row tiles and each tile
     runs against its expert's matrices — in bfloat16 on the grouped tcgen05 GEMM over rows gathered once, otherwise
     (true float32, sizes the tensor-core kernel does not take) on the exact tiled kernel, which gathers as it reads.
-    The weighted sum, the shared expert and its gate meet in one combine pass."""
+    The weighted sum, the shared expert and its gate meet in one combine pass.  Identity experts (router outputs beyond the
+    experts with matrices) are chosen like the others; their pairs run no product and their share, weight · input, is added in the
+    combine pass."""
 
     kind = "moe"
 
@@ -80,6 +98,8 @@ class MoeFeedForward:
             raise ValueError(f"unknown gated activation {spec.act!r}")
         self.spec, self.act, self.score = spec, SK.ACTIVATIONS.get(spec.act, SK.ACT_NONE), SK.SCORES[spec.score]
         E = spec.experts
+        self.n_route = E + spec.identity                   # router outputs: experts, then identity experts (no matrices)
+        self.choice_bias = w["correction"].float().contiguous() if spec.choice_bias else None
         self.u_off = self.shared_u_off = 0
         if spec.gated:                                                                  # [E, gate | up (padded to 8 rows), W]
             pairs = [_stack_rows([w[f"e{e}.gate"], w[f"e{e}.up"]]) for e in range(E)]
@@ -100,9 +120,11 @@ class MoeFeedForward:
 
     @staticmethod
     def shapes(spec: MoeMlpSpec, W: int) -> Dict[str, Tuple[int, ...]]:
-        out: Dict[str, Tuple[int, ...]] = {"router": (spec.experts, W)}
+        out: Dict[str, Tuple[int, ...]] = {"router": (spec.experts + spec.identity, W)}
         if spec.router_bias:
-            out["router.b"] = (spec.experts,)
+            out["router.b"] = (spec.experts + spec.identity,)
+        if spec.choice_bias:
+            out["correction"] = (spec.experts + spec.identity,)
         for e in range(spec.experts):
             out[f"e{e}.up"], out[f"e{e}.down"] = (spec.ff, W), (W, spec.ff)
             if spec.gated:
@@ -129,8 +151,9 @@ class MoeFeedForward:
         s = self.spec
         M, W = h.shape
         z = SK.linear(h, self.w_route)                                             # fp32 [M, router logits | gate logit]
-        idx, wt = SK.moe_route(z, s.experts, s.top, s.groups, s.keep, s.group_top, self.score, s.normalise, s.scale,
-                               bias=self.router_bias)
+        ident_w = torch.empty(M, dtype=torch.float32, device=h.device) if s.identity else None
+        idx, wt = SK.moe_route(z, self.n_route, s.top, s.groups, s.keep, s.group_top, self.score, s.normalise, s.scale,
+                               bias=self.router_bias, choice_bias=self.choice_bias, n_real=s.experts, ident_w=ident_w)
         n_up = self.up.shape[1]                                                    # ff, or gate | up rows of a gated expert
         if M <= SK.MOE_PAIR_ROWS:
             n = M * s.top
@@ -179,6 +202,8 @@ class MoeFeedForward:
             shared = SK.linear(u, self.shared_down)
             if self.gate_off >= 0:
                 gate = z[:, self.gate_off:self.gate_off + 1]
+        if s.identity:                                     # pairs that chose an identity expert ran nothing: weight · input instead
+            return SK.moe_combine(y, pos, wt, shared, gate, W, idx=idx, ident_w=ident_w, x=h)
         return SK.moe_combine(y, pos, wt, shared, gate, W)
 
 

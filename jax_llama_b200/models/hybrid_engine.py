@@ -10,7 +10,10 @@ token-at-a-time stream are inherited; what changes is
 * the block form: sublayers one after the other, each between two norms ("sandwich"), or mixer and feed-forward
   side by side on two norms of the same stream, their scaled sum added to it ("parallel"),
 * the cache: per attention layer a key / value cache with that layer's head sizes (none for a layer that reads another
-  layer's), per recurrent layer an fp32 state, all advanced by the same device-side fill level and left-pad counts,
+  layer's), per recurrent layer an fp32 state, all advanced by the same device-side fill level and left-pad counts; a
+  stretch of layers that runs several times over with the same weights (`config.loop`) has one cache entry per layer RUN,
+* the ends of a layer: a learned position row added to the token embedding, and a per-layer token input after the
+  feed-forward (a second embedding table, gated by a projection of the stream, projected up, normed and added),
 * the numerics: norms, softmax, recurrences and the residual sum in fp32; matrix operands in bfloat16, or everything in
   true float32 (`dtype=torch.float32`), which the kernels of this family are built for.
 """
@@ -42,6 +45,7 @@ class HybridCache(DeviceKVCache):
     states: List[Any] = field(default_factory=list)      # per layer: fp32 tensor(s) carried from token to token
     length: int = 0
     prev_tok: Optional[torch.Tensor] = None              # int32 [B]: every row's last token (embeddings that hash token pairs)
+    step_ids: Optional[torch.Tensor] = None              # int32 [B·S]: the tokens of the step in flight (per-layer token inputs)
 
     @property
     def capacity(self) -> int:
@@ -74,6 +78,34 @@ class HybridLayer:
     norm2: Optional[torch.Tensor] = None
     norm2b: Optional[torch.Tensor] = None
     ff: Any = None
+    side: Any = None                               # per-layer token input (`TokenSide`)
+
+
+class TokenSide:
+    """Per-layer token input: y = proj (gelu_tanh(gate x) · Es[token, col0 : col0 + dim]);  x += y / rms(y) · w.  `table` is the
+    second embedding table [vocab, layers · dim], shared by the layers; every layer reads its own slice of a row (the same
+    slice on every pass of a looped layer).  Many rows: two GEMMs around a small gate kernel, then the fused "norm, add, next
+    norm" step; a few rows (decoding): one launch that keeps the stream row in fp32 throughout."""
+
+    FUSED_ROWS = 8
+
+    def __init__(self, table: torch.Tensor, col0: int, w: Dict[str, torch.Tensor]):
+        self.table, self.col0 = table, int(col0)
+        self.gate, self.proj, self.norm = w["gate"].contiguous(), w["proj"].contiguous(), w["norm"].contiguous()
+        self.dim = self.gate.shape[0]
+
+    def weights(self) -> List[torch.Tensor]:
+        return [self.gate, self.proj, self.norm]
+
+    def run(self, x: torch.Tensor, ids: torch.Tensor, w_next: Optional[torch.Tensor], eps: float) -> Optional[torch.Tensor]:
+        """Adds the token input to x (fp32, in place); returns norm(x) · w_next when w_next is given."""
+        if x.shape[0] <= self.FUSED_ROWS:
+            return SK.token_side(x, ids, self.table, self.col0, self.gate, self.proj, self.norm, w_next, eps)
+        xc = x if self.gate.dtype == torch.float32 else SK.act_cast(x, self.gate.dtype)
+        t = SK.linear(xc, self.gate)                                          # fp32 [M, dim]
+        g = SK.side_gate(t, ids, self.table, self.col0, self.dim, self.gate.dtype)
+        y = SK.linear(g, self.proj)                                           # fp32 [M, width]
+        return SK.postnorm_add(y, self.norm, x, eps, 0.0, w_next=w_next)
 
 
 def tensor_shapes(config: Any, decay_rank: int = 16, present: Optional[Dict[str, Tuple[int, ...]]] = None
@@ -90,9 +122,16 @@ def tensor_shapes(config: Any, decay_rank: int = 16, present: Optional[Dict[str,
         out["embed.norm"] = (W,)
     if config.pair_embedding is not None:
         out["bigram"] = (config.pair_embedding.buckets + 1, W)
+    if config.learned_positions:                       # the table's own length wins over the configuration's
+        out["pos"] = (int(present["pos"][0]) if present and "pos" in present else config.max_positions, W)
+    side = config.token_side_dim
+    if side:
+        out["side.embed"] = (config.vocab_size, len(config.layers) * side)
     for i, l in enumerate(config.layers):
         p, m = f"l{i}.", l.mixer
         out[p + "norm1"] = (W,)
+        if side:
+            out[p + "side.gate"], out[p + "side.proj"], out[p + "side.norm"] = (side, W), (W, side), (W,)
         if sandwich:
             out[p + "norm1b"] = (W,)
         if hasattr(MIXERS[m.kind], "shapes"):
@@ -180,6 +219,12 @@ class HybridEngine(B200Engine):
         self.embed_norm = get("embed.norm") if config.embed_norm else None
         self.pair_table = get("bigram") if config.pair_embedding is not None else None
         self.pair_spec = config.pair_embedding
+        self.pos_table = get("pos") if config.learned_positions else None
+        self.side_table = get("side.embed") if config.token_side_dim else None
+        if (self.pos_table is not None or self.side_table is not None) and (self.pair_table is not None or config.embed_norm):
+            raise ValueError("learned positions and token inputs do not combine with a pair-hash or normed embedding")
+        if self.side_table is not None and not self.parallel:
+            raise ValueError("per-layer token inputs go with parallel blocks")
         if self.pair_table is None and self.embed_norm is not None:
             # a normed embedding without a pair table runs the same kernel over a table of zeros
             from ..config import PairEmbeddingSpec
@@ -203,7 +248,13 @@ class HybridEngine(B200Engine):
                     layer.ff = FEED_FORWARDS[l.mlp.kind](l.mlp, fw)
                 except ValueError as e:
                     raise ValueError(f"layer {i}: {e}") from None
+            if self.side_table is not None:
+                sw = {k[len(p) + 5:]: get(k) for k in want if k.startswith(p + "side.")}
+                layer.side = TokenSide(self.side_table, i * config.token_side_dim, sw)
             self.layers.append(layer)
+        # layer runs: the layer of every step through the stack (a looped stretch appears `times` times); caches and states
+        # are per run, weights per layer
+        self.runs: List[int] = list(config.layer_runs())
         self._rope: Dict[Tuple, Tuple[torch.Tensor, torch.Tensor]] = {}
         self._decode_states: Dict[Tuple[int, int], DecodeState] = {}
         self._mega_gen = torch.zeros(1, dtype=torch.int32, device=self.device)
@@ -225,8 +276,10 @@ class HybridEngine(B200Engine):
     def weight_bytes_per_step(self, rows: int = 1) -> int:
         """Bytes of weights a decode step of `rows` tokens streams (a mixture of experts: the experts it can touch)."""
         ws = [self.lm_head, self.final_norm] + [t for t in (self.embed_norm,) if t is not None]
-        for l in self.layers:
+        for l in (self.layers[i] for i in self.runs):
             ws += l.mixer.weights() + [t for t in (l.norm1, l.norm1b, l.norm2, l.norm2b) if t is not None]
+            if l.side is not None:
+                ws += l.side.weights()
             if l.ff is not None:
                 ws += l.ff.streamed_weights(rows)
         return sum(t.numel() * t.element_size() for t in ws)
@@ -247,18 +300,25 @@ class HybridEngine(B200Engine):
                                                   rot.scaling if rot is not None else None)
         return have
 
+    def _ropes(self, mixer: Any, length: int) -> Tuple[torch.Tensor, ...]:
+        """The tables a mixer's `forward` gets: cos / sin of its q / k rotation, then those of its value rotation if it has one."""
+        rope = self._rope_for(getattr(mixer.spec, "rot", None), length)
+        vrot = getattr(mixer, "value_rot", None)
+        return rope if vrot is None else rope + self._rope_for(vrot, length)
+
     def _check_max_length(self, max_length: int) -> None:
+        if self.pos_table is not None and max_length > self.pos_table.shape[0]:
+            raise ValueError(f"max_length {max_length} exceeds the {self.pos_table.shape[0]} learned positions")
         for l in self.layers:
-            rot = getattr(l.mixer.spec, "rot", None)
-            if rot is not None:
-                self._rope_for(rot, max_length)
+            if getattr(l.mixer.spec, "rot", None) is not None:
+                self._ropes(l.mixer, max_length)
 
     # ------------------------------------------------------------------ cache
     def new_cache(self, batch: int, max_length: int) -> HybridCache:
         ks: List[Optional[torch.Tensor]] = []
         vs: List[Optional[torch.Tensor]] = []
         states: List[Optional[torch.Tensor]] = []
-        for l in self.layers:
+        for l in (self.layers[i] for i in self.runs):
             kv = l.mixer.new_cache(batch, max_length, self.device)
             ks.append(kv[0] if kv is not None else None)
             vs.append(kv[1] if kv is not None else None)
@@ -272,6 +332,14 @@ class HybridEngine(B200Engine):
                            len_dev=torch.zeros(1, dtype=torch.int32, device=self.device),
                            ks=ks, vs=vs, states=states, length=int(max_length), prev_tok=prev)
 
+    def _step_ids(self, ids: torch.Tensor, cache: Optional[HybridCache]) -> torch.Tensor:
+        """The step's tokens as int32 [M]; kept with the cache for the layers that take the token itself as an input."""
+        ids32 = ids if ids.dtype == torch.int32 and ids.is_contiguous() else ids.to(torch.int32).contiguous()
+        ids32 = ids32.view(-1)
+        if cache is not None:
+            cache.step_ids = ids32
+        return ids32
+
     # ------------------------------------------------------------------ layer stack
     def _embed(self, ids: torch.Tensor, out: Optional[torch.Tensor] = None, cache: Optional[HybridCache] = None,
                B: int = 0, S: int = 0) -> torch.Tensor:
@@ -281,6 +349,12 @@ class HybridEngine(B200Engine):
                 raise ValueError("an embedding that hashes token pairs needs the cache of the request batch")
             return SK.embed_pair_norm(ids, self.embedding, self.pair_table, self.embed_norm, cache.prev_tok, cache.len_dev,
                                       cache.pad_left, B, S, pe.buckets, pe.mul_prev, pe.mul_cur, self.eps, out=out)
+        if self.pos_table is not None or self.side_table is not None:
+            if cache is None:
+                raise ValueError("learned positions and token inputs need the cache of the request batch")
+            ids = self._step_ids(ids, cache)
+        if self.pos_table is not None:
+            return SK.embed_pos(ids, self.embedding, self.pos_table, cache.len_dev, cache.pad_left, B, S, out=out)
         return SK.embed_f32(ids, self.embedding, out=out)
 
     def _head(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -299,16 +373,17 @@ class HybridEngine(B200Engine):
         if self.parallel:
             return self._layers_parallel(x, B, S, cache)
         eps, off = self.eps, self.norm_offset
-        n = len(self.layers)
-        h = SK.norm_f32(x, self.layers[0].norm1, eps, off)
-        for i, l in enumerate(self.layers):
-            rope = self._rope_for(getattr(l.mixer.spec, "rot", None), cache.capacity)
+        stack = [self.layers[i] for i in self.runs]
+        n = len(stack)
+        h = SK.norm_f32(x, stack[0].norm1, eps, off)
+        for i, l in enumerate(stack):                    # i: the run, which is also the index of its cache entries
+            rope = self._ropes(l.mixer, cache.capacity)
             z = l.mixer.forward(h, B, S, cache, i, rope)
-            nxt = l.norm2 if l.ff is not None else (self.layers[i + 1].norm1 if i + 1 < n else None)
+            nxt = l.norm2 if l.ff is not None else (stack[i + 1].norm1 if i + 1 < n else None)
             h = SK.postnorm_add(z, l.norm1b, x, eps, off, w_next=nxt)
             if l.ff is not None:
                 z = l.ff.run(h)
-                nxt = self.layers[i + 1].norm1 if i + 1 < n else None
+                nxt = stack[i + 1].norm1 if i + 1 < n else None
                 h = SK.postnorm_add(z, l.norm2b, x, eps, off, w_next=nxt)
             if self.capture_streams is not None:
                 self.capture_streams.append(x.clone())
@@ -323,15 +398,16 @@ class HybridEngine(B200Engine):
         the mixer's.  Inside a graph capture the fork and join become edges of the captured graph.  Wider steps stay on
         one stream (their tensor-core GEMMs share one split-K workspace)."""
         eps, mult = self.eps, float(self.config.residual_mult)
-        n = len(self.layers)
+        stack = [self.layers[i] for i in self.runs]
+        n = len(stack)
         overlap = B * S <= BRANCH_OVERLAP_ROWS
         main = torch.cuda.current_stream()
-        first = self.layers[0]
+        first = stack[0]
         h1, h2 = SK.branch_add_norm(x, None, None, mult, first.norm1, first.norm2 if first.ff is not None else None, eps)
-        for i, l in enumerate(self.layers):
+        for i, l in enumerate(stack):                    # i: the run, which is also the index of its cache entries
             if self.shared_norm:
                 h2 = h1
-            rope = self._rope_for(getattr(l.mixer.spec, "rot", None), cache.capacity)
+            rope = self._ropes(l.mixer, cache.capacity)
             y2 = None
             forked = overlap and l.ff is not None
             if forked:
@@ -346,9 +422,17 @@ class HybridEngine(B200Engine):
                 main.wait_event(join)
             elif l.ff is not None:
                 y2 = l.ff.run(h2)
-            nxt = self.layers[i + 1] if i + 1 < n else None
-            h1, h2 = SK.branch_add_norm(x, y1, y2, mult, nxt.norm1 if nxt is not None else None,
-                                        nxt.norm2 if nxt is not None and nxt.ff is not None else None, eps)
+            nxt = stack[i + 1] if i + 1 < n else None
+            w1 = nxt.norm1 if nxt is not None else None
+            w2 = nxt.norm2 if nxt is not None and nxt.ff is not None else None
+            if l.side is None:
+                h1, h2 = SK.branch_add_norm(x, y1, y2, mult, w1, w2, eps)
+            else:
+                # the token input reads the stream after both branches were added, and forms the next block's norm itself
+                SK.branch_add_norm(x, y1, y2, mult, None, None, eps)
+                h1 = l.side.run(x, cache.step_ids, w1 if self.shared_norm else None, eps)
+                if not self.shared_norm and nxt is not None:
+                    h1, h2 = SK.branch_add_norm(x, None, None, mult, w1, w2, eps)
             if self.capture_streams is not None:
                 self.capture_streams.append(x.clone())
         return x

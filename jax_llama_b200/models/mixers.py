@@ -17,7 +17,7 @@ from typing import Dict, List, Optional, Tuple
 import torch
 
 from ..config import (AttentionMixerSpec, DeltaMixerSpec, GlaMixerSpec, LatentAttentionMixerSpec, ParallelMixerSpec,
-                      RetentionMixerSpec, RotaryScaling, StateSpaceMixerSpec)
+                      RetentionMixerSpec, RotaryScaling, RotarySpec, StateSpaceMixerSpec)
 from ..ops import _lib
 from ..ops import kernels as K
 from ..ops import seq_kernels as SK
@@ -98,7 +98,13 @@ class AttentionMixer(Mixer):
     With mixed weights head h's output is Σ_j (Σ_g T[h, g] p_g(j)) v_c(j) = Σ_g T[h, g] (Σ_j p_g(j) v_c(j)), c its own
     key/value head: the attention kernel forms, per query head g, the weighted sums over the values of ALL key/value heads
     (the value cache is token-major, one row [kv_heads · vdim] per token, read as one wide value head) in fp32, and a
-    second small kernel mixes them.  The sink's share is not mixed: it has no values."""
+    second small kernel mixes them.  The sink's share is not mixed: it has no values.
+
+    Further options, all parameters of the spec: an RMS norm with a weight on every q / k head before the rotation (`qk_norm`),
+    either pairing of the rotated channels (`rot.layout`), values rotated at their own position and the head's sum rotated back
+    at the query's (`v_rot`: the value cache holds rotated values, so a cached value never has to be touched again and the
+    weighted sum depends on relative positions only), blocks of `chunk` positions instead of (or besides) a window, and a
+    learned sink logit per head.  These run the masked form of the generic attention kernels."""
 
     kind = "attention"
 
@@ -122,7 +128,17 @@ class AttentionMixer(Mixer):
         self.talk = w["talk"].contiguous() if spec.talking_heads else None
         if spec.talking_heads and (self.shares_kv or spec.head_gate):
             raise ValueError("mixed attention weights go with a layer's own keys / values and no head gate")
-        self.plain = not (spec.bias or spec.v_unit_norm or spec.window or spec.sink or spec.talking_heads)
+        self.plain = not (spec.bias or spec.v_unit_norm or spec.window or spec.sink or spec.talking_heads or spec.qk_norm
+                          or spec.chunk or spec.v_rot or (spec.rot is not None and spec.rot.layout != "interleaved"))
+        self.q_norm = w["q.norm"].contiguous() if spec.qk_norm else None
+        self.k_norm = w["k.norm"].contiguous() if spec.qk_norm and not self.shares_kv else None
+        self.sink_logit = w["sink"].float().contiguous() if spec.sink_learned else None
+        if spec.sink_learned and not spec.sink:
+            raise ValueError("a learned sink logit needs the sink")
+        if spec.v_rot and (spec.rot is None or spec.vdim % 2 or spec.talking_heads or spec.v_unit_norm or self.shares_kv):
+            raise ValueError("rotated values need a rotary spec, an even vdim and a layer's own head-major value cache")
+        # the rotation of the values: all vdim channels, the base and pairing of the q / k rotation, no interpolation
+        self.value_rot = RotarySpec(spec.vdim, spec.rot.base, spec.rot.layout, None) if spec.v_rot else None
 
     @staticmethod
     def shapes(spec: AttentionMixerSpec, W: int, rank_of: "object" = None) -> Dict[str, Tuple[int, ...]]:
@@ -137,10 +153,16 @@ class AttentionMixer(Mixer):
                     out[n + ".b"] = (out[n][0],)
         if spec.talking_heads:
             out["talk"] = (spec.heads, spec.heads)
+        if spec.qk_norm:
+            out["q.norm"] = (spec.dim,)
+            if spec.kv_from is None:
+                out["k.norm"] = (spec.dim,)
+        if spec.sink_learned:
+            out["sink"] = (spec.heads,)
         return out
 
     def weights(self) -> List[torch.Tensor]:
-        return [self.w_in, self.wo] + ([self.talk] if self.talk is not None else [])
+        return [self.w_in, self.wo] + [t for t in (self.talk, self.q_norm, self.k_norm, self.sink_logit) if t is not None]
 
     def new_cache(self, batch: int, length: int, device: torch.device) -> Optional[Tuple[torch.Tensor, torch.Tensor]]:
         if self.shares_kv:
@@ -163,16 +185,21 @@ class AttentionMixer(Mixer):
         src = layer if not self.shares_kv else s.kv_from
         kc, vc = cache.ks[src], cache.vs[src]
         rot = s.rot.dims if s.rot is not None else 0
+        layout = SK.ROT_LAYOUTS[s.rot.layout] if s.rot is not None else 0
+        v_cos, v_sin = (rope[2], rope[3]) if s.v_rot else (None, None)      # the engine appends the tables of `value_rot`
         SK.attn_prep(y, self.q_off, self.k_off, self.v_off, q, None if self.shares_kv else kc,
                      None if self.shares_kv else vc, rope[0], rope[1], rot, s.qk_unit_norm, self.eps, cache.len_dev,
                      cache.pad_left, B, S, s.heads, s.kv_heads, s.dim, s.vdim, bias=self.bias, v_unit_norm=s.v_unit_norm,
-                     v_token_major=s.talking_heads)
+                     v_token_major=s.talking_heads, layout=layout, q_norm_w=self.q_norm,
+                     k_norm_w=self.k_norm if self.k_norm is not None else self.q_norm, v_cos=v_cos, v_sin=v_sin)
         if s.talking_heads:
             return self._attend_mixed(q, kc, vc, cache, B, S)
         gate = y[:, self.g_off:self.g_off + s.heads] if s.head_gate else None
+        if not self.plain and (gate is not None or s.chunk or s.sink_learned or s.v_rot):
+            return SK.attn_masked(q, kc, vc, cache.len_dev, cache.pad_left, B, S, s.heads, s.kv_heads, s.dim, s.vdim, s.scale,
+                                  gate=gate, window=s.window, chunk=s.chunk, sink=s.sink, sink_logit=self.sink_logit,
+                                  v_cos=v_cos, v_sin=v_sin, v_layout=layout)
         if not self.plain:
-            if gate is not None:
-                raise NotImplementedError("a head gate with a window or a sink")
             T = kc.shape[2]
             return SK.attn_windowed(q, kc, vc, cache.len_dev, cache.pad_left, B, S, s.heads, s.kv_heads, s.dim, s.vdim, T,
                                     s.dim, s.vdim, s.window, s.scale, sink=s.sink)

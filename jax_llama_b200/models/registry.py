@@ -9,7 +9,7 @@ import json
 import os
 from typing import Any, Callable, Dict, Optional, Tuple
 
-from ..config import CONFIG_NAME, BazulornConfig, FoliraxConfig, LLaMAConfig, NikonexConfig
+from ..config import CONFIG_NAME, BazulornConfig, DatozenConfig, FoliraxConfig, LLaMAConfig, NikonexConfig
 
 _REGISTRY: Dict[str, Tuple[Any, Callable[[], Any]]] = {}
 _KERNEL_SUBSET: Dict[str, Optional[str]] = {}
@@ -54,10 +54,16 @@ def _bazulorn() -> Any:
     return BazulornForCausalLM
 
 
+def _datozen() -> Any:
+    from .datozen import DatozenForCausalLM
+    return DatozenForCausalLM
+
+
 register("llama", LLaMAConfig, _llama)
 register("folirax", FoliraxConfig, _folirax, kernel_subset="hybrid", dtypes=("bfloat16", "float32"))
 register("nikonex", NikonexConfig, _nikonex, kernel_subset="hybrid", dtypes=("bfloat16", "float32"))
 register("bazulorn", BazulornConfig, _bazulorn, kernel_subset="hybrid", dtypes=("bfloat16", "float32"))
+register("datozen", DatozenConfig, _datozen, kernel_subset="hybrid", dtypes=("bfloat16", "float32"))
 
 
 def architecture_of(config: Dict[str, Any]) -> str:

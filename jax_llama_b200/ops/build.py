@@ -25,13 +25,13 @@ LIB_PATH = OUT_DIR / "libjllama_b200.so"
 STAMP = OUT_DIR / "build.stamp"
 
 # Sources whose arithmetic has to be exact float32 (true division, expf, tanhf, sqrtf): built without --use_fast_math.
-PRECISE_SOURCES = {"seq_norm.cu", "seq_linear.cu", "attn_generic.cu", "gla_scan.cu", "moe.cu", "seq_mix.cu", "delta_scan.cu"}
+PRECISE_SOURCES = {"seq_norm.cu", "seq_linear.cu", "attn_generic.cu", "gla_scan.cu", "moe.cu", "seq_mix.cu", "delta_scan.cu", "seq_token.cu"}
 
 # Named subsets of the library: a model family that needs only some kernels gets a small library of its own at the
 # first use in a fresh tree (seconds instead of the minutes of the whole-step decode kernels).  The full library
 # contains every subset; `ops/_lib.py` prefers it when it is already built.
 SUBSETS = {
-    "hybrid": ["error.cu", "seq_norm.cu", "seq_linear.cu", "attn_generic.cu", "gla_scan.cu", "moe.cu", "seq_mix.cu", "delta_scan.cu", "sample_full.cu",
+    "hybrid": ["error.cu", "seq_norm.cu", "seq_linear.cu", "attn_generic.cu", "gla_scan.cu", "moe.cu", "seq_mix.cu", "delta_scan.cu", "seq_token.cu", "sample_full.cu",
                "gemm_tcgen05.cu", "gemm_2cta.cu", "tensormap.cu", "flash_prefill.cu", "prefill_attn_mma.cu", "decode_attn.cu"],
 }
 

@@ -16,10 +16,11 @@ import torch
 from . import _lib
 from .kernels import _p, _stream, ensure_gemm_workspace, num_sms
 
-ACT_NONE, ACT_RELU2, ACT_GELU_TANH, ACT_SILU, ACT_SCALE_SOFTCAP, ACT_SIGMOID = 0, 1, 2, 3, 4, 5
+ACT_NONE, ACT_RELU2, ACT_GELU_TANH, ACT_SILU, ACT_SCALE_SOFTCAP, ACT_SIGMOID, ACT_XIELU = 0, 1, 2, 3, 4, 5, 6
 DELTA_FUSED_MAX_TOKENS = 8    # the same for the delta-rule scan (csrc/delta_scan.cu DS_FUSED_MAX_TOKENS)
 GLA_FUSED_MAX_TOKENS = 8      # up to this many tokens per row the gated-linear-attention scan stays one fused launch
-ACTIVATIONS = {"none": ACT_NONE, "relu2": ACT_RELU2, "gelu_tanh": ACT_GELU_TANH, "silu": ACT_SILU, "sigmoid": ACT_SIGMOID}
+ACTIVATIONS = {"none": ACT_NONE, "relu2": ACT_RELU2, "gelu_tanh": ACT_GELU_TANH, "silu": ACT_SILU, "sigmoid": ACT_SIGMOID,
+               "xielu": ACT_XIELU}         # xielu takes two numbers (p0, p1): z > 0: p0 z^2 + z/2, else p1 (e^z - 1 - z) + z/2
 GLU_PRODUCT, GLU_CLAMPED = 0, 1         # act(gate) * up;  g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit), u' = clamp(u, ±limit)
 
 
@@ -148,14 +149,25 @@ def attn_prep(y: torch.Tensor, q_off: int, k_off: int, v_off: int, q_out: torch.
               k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], cos: torch.Tensor, sin: torch.Tensor,
               rot: int, unit_norm: bool, eps: float, cache_len: torch.Tensor, pad_left: Optional[torch.Tensor],
               B: int, S: int, H: int, G: int, D: int, Dv: int, bias: Optional[torch.Tensor] = None, v_unit_norm: bool = False,
-              v_token_major: bool = False) -> None:
+              v_token_major: bool = False, layout: int = 0, q_norm_w: Optional[torch.Tensor] = None,
+              k_norm_w: Optional[torch.Tensor] = None, v_cos: Optional[torch.Tensor] = None, v_sin: Optional[torch.Tensor] = None
+              ) -> None:
     """Rotate / normalise q (and k), append k, v to the caches [B, G, T, D] / [B, G, T, Dv].  k_off < 0: queries only.
     bias: fp32 over the columns of y, added first; v_unit_norm: values scaled to unit RMS per head before they are cached;
-    v_token_major: the value cache is [B, T, G·Dv]."""
+    v_token_major: the value cache is [B, T, G·Dv].  layout: pairing of the rotated channels (ROT_INTERLEAVED / ROT_HALF);
+    q_norm_w / k_norm_w [D]: an RMS norm with a weight on every head BEFORE the rotation; v_cos / v_sin fp32 [positions, Dv/2]:
+    values are rotated at their own position over all their channels (same pairing) before they are cached."""
     _need(y, torch.float32, "y")
     if bias is not None:
         _need(bias, torch.float32, "bias")
     T_cap = k_cache.shape[2] if k_cache is not None else 0
+    if layout or q_norm_w is not None or v_cos is not None:
+        _lib.check(_lib.lib().jl_attn_prep_ex(
+            y.data_ptr(), y.stride(0), q_off, k_off, v_off, q_out.data_ptr(), _p(k_cache), _p(v_cache), cos.data_ptr(),
+            sin.data_ptr(), cos.shape[0], rot, int(layout), int(unit_norm), _p(q_norm_w), _p(k_norm_w), float(eps), _p(v_cos),
+            _p(v_sin), v_cos.shape[0] if v_cos is not None else 0, int(layout), _p(cache_len), _p(pad_left), B, S, H, G, D, Dv,
+            T_cap, _p(bias), int(v_unit_norm), int(v_token_major), dtype_code(q_out.dtype), _stream()), "jl_attn_prep_ex")
+        return
     _lib.check(_lib.lib().jl_attn_prep(
         y.data_ptr(), y.stride(0), q_off, k_off, v_off, q_out.data_ptr(), _p(k_cache), _p(v_cache), cos.data_ptr(),
         sin.data_ptr(), cos.shape[0], rot, int(unit_norm), float(eps), _p(cache_len), _p(pad_left), B, S, H, G, D, Dv,
@@ -321,6 +333,36 @@ def attn_windowed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     return out
 
 
+def attn_masked(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, cache_len: torch.Tensor,
+                pad_left: Optional[torch.Tensor], B: int, S: int, H: int, G: int, D: int, Dv: int, scale: float, *,
+                gate: Optional[torch.Tensor] = None, window: int = 0, chunk: int = 0, sink: bool = False,
+                sink_logit: Optional[torch.Tensor] = None, v_cos: Optional[torch.Tensor] = None,
+                v_sin: Optional[torch.Tensor] = None, v_layout: int = 0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Causal attention of S new tokens per row over caches [B, G, T, D] / [B, G, T, Dv] with everything the kernels take:
+    gate fp32 view [M, H] (sigmoid per head on the output); window; chunk > 0: positions form blocks of `chunk` and a query sees
+    the keys of its own block only; sink with an optional learned logit per head (fp32 [H]); v_cos / v_sin fp32
+    [positions, Dv/2]: the values were cached rotated at their own positions and every head's sum is rotated back by the
+    query's position, before the gate."""
+    T_cap = k_cache.shape[2]
+    if out is None:
+        out = torch.empty((B * S, H * Dv), dtype=q.dtype, device=q.device)
+    if sink_logit is not None:
+        _need(sink_logit, torch.float32, "sink_logit")
+    L = _lib.lib()
+    splits, scratch = 0, None
+    if S == 1:
+        reach = min([T_cap] + [int(v) for v in (window, chunk) if v > 0])
+        splits = int(L.jl_attn_generic_splits(B, H, G, reach))
+        if splits:
+            scratch = torch.empty(B * H * splits * (Dv + 2), dtype=torch.float32, device=q.device)
+    _lib.check(L.jl_attn_masked(
+        q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), _p(gate), gate.stride(0) if gate is not None else 0,
+        _p(cache_len), _p(pad_left), B, S, H, G, D, Dv, T_cap, D, Dv, 0, 0, 0, 0, int(window), int(chunk), float(scale), _p(scratch),
+        splits, int(sink), _p(sink_logit), _p(v_cos), _p(v_sin), v_cos.shape[0] if v_cos is not None else 0, int(v_layout), 0,
+        dtype_code(q.dtype), _stream()), "jl_attn_masked")
+    return out
+
+
 def retention_scan(y: torch.Tensor, q_off: int, k_off: int, v_off: int, head_decay: torch.Tensor, cos: torch.Tensor,
                    sin: torch.Tensor, rot: int, layout: int, k_scale: float, state: torch.Tensor,
                    cache_len: Optional[torch.Tensor], pad_left: Optional[torch.Tensor], B: int, S: int, H: int, D: int,
@@ -344,12 +386,20 @@ def retention_scan(y: torch.Tensor, q_off: int, k_off: int, v_off: int, head_dec
 
 
 def moe_route(z: torch.Tensor, E: int, top: int, groups: int, keep: int, group_top: int, score: int, normalise: bool,
-              scale: float, bias: Optional[torch.Tensor] = None) -> "tuple[torch.Tensor, torch.Tensor]":
-    """fp32 router logits (columns 0..E-1 of z, plus the fp32 `bias` [E]) → (experts int32 [M, top], weights fp32 [M, top])."""
+              scale: float, bias: Optional[torch.Tensor] = None, choice_bias: Optional[torch.Tensor] = None, n_real: Optional[int] = None,
+              ident_w: Optional[torch.Tensor] = None) -> "tuple[torch.Tensor, torch.Tensor]":
+    """fp32 router logits (columns 0..E-1 of z, plus the fp32 `bias` [E]) → (experts int32 [M, top], weights fp32 [M, top]).
+    choice_bias fp32 [E]: added to the scores for the choice (group scores and top) only.  n_real < E: the router outputs from
+    n_real on are identity experts; a chosen one is reported as expert -1 and its weight is added to ident_w fp32 [M]."""
     _need(z, torch.float32, "z")
     M = z.shape[0]
     idx = torch.empty((M, top), dtype=torch.int32, device=z.device)
     wt = torch.empty((M, top), dtype=torch.float32, device=z.device)
+    if choice_bias is not None or (n_real is not None and n_real != E):
+        _lib.check(_lib.lib().jl_moe_route_ex(z.data_ptr(), z.stride(0), M, E, top, groups, keep, group_top, score, int(normalise),
+                                              float(scale), _p(bias), _p(choice_bias), E if n_real is None else int(n_real),
+                                              _p(ident_w), idx.data_ptr(), wt.data_ptr(), _stream()), "jl_moe_route_ex")
+        return idx, wt
     _lib.check(_lib.lib().jl_moe_route(z.data_ptr(), z.stride(0), M, E, top, groups, keep, group_top, score, int(normalise),
                                        float(scale), _p(bias), idx.data_ptr(), wt.data_ptr(), _stream()), "jl_moe_route")
     return idx, wt
@@ -405,10 +455,19 @@ def gemm_grouped(x: torch.Tensor, w: torch.Tensor, tile_group: torch.Tensor, *, 
 
 
 def moe_combine(z: torch.Tensor, pos: Optional[torch.Tensor], wt: torch.Tensor, shared: Optional[torch.Tensor],
-                gate: Optional[torch.Tensor], W: int) -> torch.Tensor:
-    """Σ_k wt[m, k] · z[pos[m, k]] (+ sigmoid(gate[m]) · shared[m]) → fp32 [M, W]; gate: fp32 view [M, 1] (any pitch)."""
+                gate: Optional[torch.Tensor], W: int, idx: Optional[torch.Tensor] = None, ident_w: Optional[torch.Tensor] = None,
+                x: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Σ_k wt[m, k] · z[pos[m, k]] (+ sigmoid(gate[m]) · shared[m]) → fp32 [M, W]; gate: fp32 view [M, 1] (any pitch).
+    With `idx` the pairs whose expert is < 0 are skipped, and ident_w[m] · x[m] (identity experts) is added."""
     M, top = wt.shape
     out = torch.empty((M, W), dtype=torch.float32, device=z.device)
+    if idx is not None:
+        _lib.check(_lib.lib().jl_moe_combine_ex(z.data_ptr(), z.stride(0), _p(pos), wt.data_ptr(), top, _p(shared),
+                                                shared.stride(0) if shared is not None else 0, _p(gate),
+                                                gate.stride(0) if gate is not None else 0, out.data_ptr(), M, W, idx.data_ptr(),
+                                                _p(ident_w), _p(x), x.stride(0) if x is not None else 0,
+                                                dtype_code(x.dtype) if x is not None else 1, _stream()), "jl_moe_combine_ex")
+        return out
     _lib.check(_lib.lib().jl_moe_combine(z.data_ptr(), z.stride(0), _p(pos), wt.data_ptr(), top, _p(shared),
                                          shared.stride(0) if shared is not None else 0, _p(gate),
                                          gate.stride(0) if gate is not None else 0, out.data_ptr(), M, W, _stream()),
@@ -535,3 +594,44 @@ def delta_scan(u: torch.Tensor, q_off: int, k_off: int, v_off: int, G: int, y: t
                                _p(cache_len), _p(pad_left), B, S, H, D, Dv, R, _p(ws), dtype_code(a2.dtype), _stream()),
                "jl_delta_scan")
     return out
+
+
+# --------------------------------------------------------------------------- learned positions, per-layer token input
+def embed_pos(ids: torch.Tensor, table: torch.Tensor, pos_table: torch.Tensor, cache_len: Optional[torch.Tensor],
+              pad_left: Optional[torch.Tensor], B: int, S: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """table[id] + pos_table[position] as fp32 [B·S, W]; token (b, s) is at position *cache_len + s − pad_left[b]."""
+    ids32 = ids if ids.dtype == torch.int32 and ids.is_contiguous() else ids.to(torch.int32).contiguous()
+    V, W = table.shape
+    if out is None:
+        out = torch.empty((B * S, W), dtype=torch.float32, device=table.device)
+    _lib.check(_lib.lib().jl_embed_pos(ids32.data_ptr(), table.data_ptr(), pos_table.data_ptr(), out.data_ptr(), _p(cache_len),
+                                       _p(pad_left), B, S, W, V, pos_table.shape[0], dtype_code(table.dtype), _stream()),
+               "jl_embed_pos")
+    return out
+
+
+def side_gate(t: torch.Tensor, ids: torch.Tensor, side: torch.Tensor, col0: int, n: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """gelu_tanh(t[m, c]) · side[ids[m], col0 + c] for c < n; t fp32 [M, ≥ n]; ids int32 [M]; the result in `out_dtype`."""
+    _need(t, torch.float32, "t")
+    _need(ids, torch.int32, "ids")
+    M = t.shape[0]
+    out = torch.empty((M, n), dtype=out_dtype, device=t.device)
+    _lib.check(_lib.lib().jl_side_gate(t.data_ptr(), t.stride(0), ids.data_ptr(), side.data_ptr(), side.stride(0), int(col0),
+                                       out.data_ptr(), out.stride(0), M, int(n), side.shape[0], dtype_code(out_dtype), _stream()),
+               "jl_side_gate")
+    return out
+
+
+def token_side(x: torch.Tensor, ids: torch.Tensor, side: torch.Tensor, col0: int, w_gate: torch.Tensor, w_proj: torch.Tensor,
+               w_side: torch.Tensor, w_next: Optional[torch.Tensor], eps: float) -> Optional[torch.Tensor]:
+    """One launch for a few rows: y = w_proj (gelu_tanh(w_gate x) · side[ids, col0 : col0 + n]); x += y / rms(y) · w_side in
+    place (fp32); returns x / rms(x) · w_next in the weights' dtype when w_next is given."""
+    _need(x, torch.float32, "x")
+    _need(ids, torch.int32, "ids")
+    M, W = x.shape
+    n = w_gate.shape[0]
+    h = torch.empty((M, W), dtype=w_next.dtype, device=x.device) if w_next is not None else None
+    _lib.check(_lib.lib().jl_token_side(x.data_ptr(), ids.data_ptr(), side.data_ptr(), side.stride(0), int(col0), w_gate.data_ptr(),
+                                        w_proj.data_ptr(), w_side.data_ptr(), _p(w_next), _p(h), M, W, n, side.shape[0], float(eps),
+                                        dtype_code(w_gate.dtype), _stream()), "jl_token_side")
+    return h
