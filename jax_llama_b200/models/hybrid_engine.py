@@ -306,8 +306,14 @@ class HybridEngine(B200Engine):
         vrot = getattr(mixer, "value_rot", None)
         return rope if vrot is None else rope + self._rope_for(vrot, length)
 
+    @property
+    def position_limit(self) -> Optional[int]:
+        """The most positions a sequence can have (a learned position table has that many rows), None when nothing bounds it."""
+        return int(self.pos_table.shape[0]) if self.pos_table is not None else None
+
     def _check_max_length(self, max_length: int) -> None:
-        if self.pos_table is not None and max_length > self.pos_table.shape[0]:
+        # a sequence of max_length tokens feeds max_length - 1 of them to the model: the last one is only ever an output
+        if self.pos_table is not None and max_length - 1 > self.pos_table.shape[0]:
             raise ValueError(f"max_length {max_length} exceeds the {self.pos_table.shape[0]} learned positions")
         for l in self.layers:
             if getattr(l.mixer.spec, "rot", None) is not None:

@@ -46,7 +46,12 @@ def _open_batch(engine: Any, entries: List[Dict[str, Any]], max_tokens: int) -> 
         ids[b, S - n:] = torch.tensor(e["tokens"], dtype=torch.long)
         mask[b, S - n:] = 1
         want_rows += [b * S + (S - n) + int(w) for w in e.get("want", [])]
-    max_len = S + max(int(max_tokens), 1) + 1
+    # slots of the batch: the longest prompt plus what the token budget leaves for decoding, one to spare; never more than the
+    # model has positions for
+    max_len = S + max(int(max_tokens) - S, 1) + 1
+    limit = getattr(engine, "position_limit", None)
+    if limit is not None and S <= limit:
+        max_len = min(max_len, int(limit) + 1)            # the last slot holds a token that is never fed back
     while (B, max_len) in engine._decode_states:          # a live batch of the same shape keeps its own state
         max_len += 1
     dev = engine.device
