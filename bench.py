@@ -186,10 +186,10 @@ def main() -> None:
     ap.add_argument("--no-tp-check", action="store_true", help="skip the pre-run TP-vs-single-GPU correctness check")
     ap.add_argument("--sweep-batches", default="", help="comma-separated extra batch sizes measured with the same engine "
                     "after the headline run (device-timed decode + prefill); reported under \"batch_sweep\"")
-    ap.add_argument("--compare", default="", choices=["", "folirax", "nikonex", "bazulorn"],
+    ap.add_argument("--compare", default="", choices=["", "folirax", "nikonex", "bazulorn", "datozen"],
                     help="instead of the headline run: prefill / decode throughput of that design at layer sizes of real "
                     "models (random weights) beside the closest existing model of equal size (folirax: LLaMA; nikonex: "
-                    "Folirax; bazulorn: Nikonex), and its kernels beside the like kernels with their roofline fractions; prints one JSON line "
+                    "Folirax; bazulorn: Nikonex; datozen: Bazulorn), and its kernels beside the like kernels with their roofline fractions; prints one JSON line "
                     "of its own")
     ap.add_argument("--compare-sizes", default="w2048,w4096")
     args = ap.parse_args()
@@ -197,7 +197,7 @@ def main() -> None:
         import torch
         from jax_llama_b200.utils import compare_bench
         torch.cuda.set_device(0)
-        fn = {"nikonex": compare_bench.run_nikonex, "bazulorn": compare_bench.run_bazulorn}.get(args.compare, compare_bench.run)
+        fn = {"nikonex": compare_bench.run_nikonex, "bazulorn": compare_bench.run_bazulorn, "datozen": compare_bench.run_datozen}.get(args.compare, compare_bench.run)
         print(json.dumps(fn(args.compare_sizes.split(","), prompt_len=args.prompt_len, steps=min(args.steps, 64),
                             warmup=max(args.warmup, 3))))
         return

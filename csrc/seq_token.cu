@@ -3,9 +3,8 @@
 //  * embed_pos_kernel  — token embedding plus a learned position row: x = E[token] + P[position], into the fp32 stream.
 //  * side_gate_kernel  — the gate of a per-layer token input: g = gelu_tanh(t) * Es[token, col0 .. col0 + n), t the fp32
 //    product of a small projection with the stream, Es a second embedding table whose row holds one slice per layer.
-//  * token_side_kernel — the whole per-layer token input for a few rows (decoding), one CTA per row:
-//    y = Wp (gelu_tanh(Wg x) * Es[token, slice]);  x += y / rms(y) * w_side;  h = x / rms(x) * w_next.
-//    The stream row stays fp32 throughout (the projections read it as it is; only the weights are in the operand type).
+//  * side_gate_rows_kernel — the same gate for a few rows (decoding) with the small projection inside: a warp per gate channel
+//    streams its row of the projection against the fp32 stream rows of all tokens (the stream is not rounded first).
 //
 // Token (b, s) of a call sits at slot *cache_len + s and position slot - pad_left[b]; negative positions are padding.
 #include <stdint.h>
@@ -53,54 +52,55 @@ __global__ void __launch_bounds__(256) side_gate_kernel(const float* __restrict_
   }
 }
 
-constexpr int TS_THREADS = 256;
+constexpr int SG_WARPS = 4, SG_MAXM = 8;
 
-// One CTA per row.  Shared memory: the stream row [W] | the gate vector [n] | reduction scratch.
-template <typename T>
-__global__ void __launch_bounds__(TS_THREADS) token_side_kernel(float* __restrict__ x, const int* __restrict__ ids,
-                                                                const T* __restrict__ side, int lds, int col0,
-                                                                const T* __restrict__ wg, const T* __restrict__ wp,
-                                                                const T* __restrict__ w_side, const T* __restrict__ w_next,
-                                                                T* __restrict__ h, int W, int n, int V, float eps) {
+// A few rows (decoding): a warp per gate channel c streams row c of the gate projection once (16-byte loads) against the fp32
+// stream rows of all M tokens, then applies gelu_tanh and the token's table entry.  The stream is read as it is (no rounding
+// to the operand type); n / SG_WARPS CTAs share the weight matrix between them.
+template <typename T, int M>
+__global__ void __launch_bounds__(SG_WARPS * 32) side_gate_rows_kernel(const float* __restrict__ x, int ldx, const int* __restrict__ ids,
+                                                                       const T* __restrict__ side, int lds, int col0,
+                                                                       const T* __restrict__ wg, T* __restrict__ out, int ldo,
+                                                                       int W, int n, int V, int vec_ok) {
   pdl_wait();                      // programmatic dependent launch: nothing is read before the predecessor is done
   pdl_launch_dependents();
-  extern __shared__ float sm[];
-  __shared__ float red[33];
-  float* xs = sm;                  // [W]
-  float* gs = sm + W;              // [n]
-  const int m = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  float* xr = x + (size_t)m * W;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) xs[i] = xr[i];
-  __syncthreads();
-  int tok = ids[m];
-  tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);
-  for (int c = warp; c < n; c += TS_THREADS / 32) {      // a warp per gate channel: Wg[c, :] . x
-    const T* wr = wg + (size_t)c * W;
-    float d = 0.0f;
-    for (int i = lane; i < W; i += 32) d = fmaf(to_f(wr[i]), xs[i], d);
-    d = warp_sum(d);
-    if (lane == 0) gs[c] = apply_act(d, ACT_GELU_TANH, 0.0f, 0.0f) * to_f(side[(size_t)tok * lds + col0 + c]);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int c = blockIdx.x * SG_WARPS + warp;
+  if (c >= n) return;
+  const T* wr = wg + (size_t)c * W;
+  float acc[M];
+#pragma unroll
+  for (int m = 0; m < M; ++m) acc[m] = 0.0f;
+  int done = 0;
+  if (vec_ok) {
+    const int kv = W / 4 * 4;
+    for (int k = lane * 4; k < kv; k += 128) {
+      float wv[4];
+      load4(wr + k, wv);
+#pragma unroll
+      for (int m = 0; m < M; ++m) {
+        float xv[4];
+        load4(x + (size_t)m * ldx + k, xv);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[m] = fmaf(wv[j], xv[j], acc[m]);
+      }
+    }
+    done = kv;
   }
-  __syncthreads();
-  float ss = 0.0f;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) {    // a thread per output channel: Wp[i, :] . g (y)
-    const T* wr = wp + (size_t)i * n;
-    float d = 0.0f;
-    for (int c = 0; c < n; ++c) d = fmaf(to_f(wr[c]), gs[c], d);
-    xr[i] = d;                                           // parked in the row's own slot until the norm is known (xs holds x)
-    ss += d * d;
+  for (int k = done + lane; k < W; k += 32) {
+    const float wv = to_f(wr[k]);
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc[m] = fmaf(wv, x[(size_t)m * ldx + k], acc[m]);
   }
-  const float r = 1.0f / sqrtf(block_sum(ss, red) / (float)W + eps);
-  float s2 = 0.0f;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) {    // each thread re-reads the elements it wrote itself
-    const float v = xs[i] + xr[i] * r * to_f(w_side[i]);
-    xr[i] = v;
-    xs[i] = v;
-    s2 += v * v;
+#pragma unroll
+  for (int m = 0; m < M; ++m) {
+    const float d = warp_sum(acc[m]);
+    if (lane == 0) {
+      int tok = ids[m];
+      tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);
+      out[(size_t)m * ldo + c] = from_f<T>(apply_act(d, ACT_GELU_TANH, 0.0f, 0.0f) * to_f(side[(size_t)tok * lds + col0 + c]));
+    }
   }
-  if (w_next == nullptr) return;
-  const float r2 = 1.0f / sqrtf(block_sum(s2, red) / (float)W + eps);
-  for (int i = threadIdx.x; i < W; i += blockDim.x) h[(size_t)m * W + i] = from_f<T>(xs[i] * r2 * to_f(w_next[i]));
 }
 
 }  // namespace jl
@@ -128,19 +128,19 @@ extern "C" JL_API int jl_side_gate(const float* t, int ldt, const int* ids, cons
   return JL_OK;
 }
 
-extern "C" JL_API int jl_token_side(float* x, const int* ids, const void* side, int lds, int col0, const void* w_gate, const void* w_proj,
-                                    const void* w_side, const void* w_next, void* h, int M, int W, int n, int V, float eps, int dtype,
-                                    void* stream) {
-  JL_CHECK_ARG(M >= 1 && W >= 1 && n >= 1 && V >= 1 && col0 >= 0 && lds >= col0 + n, "jl_token_side: bad shape M=%d W=%d n=%d", M, W, n);
-  JL_CHECK_ARG((w_next == nullptr) == (h == nullptr), "jl_token_side: w_next and h come together");
-  const size_t smem = (size_t)(W + n) * sizeof(float);
-  JL_CHECK_ARG(smem <= 200 * 1024, "jl_token_side: a row of %d + %d floats does not fit shared memory", W, n);
-  JL_DISPATCH_DTYPE(dtype, {
-    if (smem > 48 * 1024)
-      JL_CUDA(cudaFuncSetAttribute(token_side_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    JL_LAUNCH_PDL(token_side_kernel<T>, dim3(M), dim3(TS_THREADS), smem, (cudaStream_t)stream, x, ids, (const T*)side, lds, col0,
-                  (const T*)w_gate, (const T*)w_proj, (const T*)w_side, (const T*)w_next, (T*)h, W, n, V, eps);
-  });
+extern "C" JL_API int jl_side_gate_rows(const float* x, int ldx, const int* ids, const void* side, int lds, int col0, const void* w_gate,
+                                        void* out, int ldo, int M, int W, int n, int V, int dtype, void* stream) {
+  JL_CHECK_ARG(M >= 1 && M <= SG_MAXM && W >= 1 && n >= 1 && V >= 1 && ldx >= W && ldo >= n && col0 >= 0 && lds >= col0 + n,
+               "jl_side_gate_rows: bad shape M=%d W=%d n=%d ldx=%d ldo=%d", M, W, n, ldx, ldo);
+  const int vec_ok = W % 4 == 0 && ldx % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w_gate % 16 == 0;
+  const dim3 grid((n + SG_WARPS - 1) / SG_WARPS);
+#define JL_SG(MM)                                                                                                            \
+  case MM:                                                                                                                   \
+    JL_DISPATCH_DTYPE(dtype, JL_LAUNCH_PDL((side_gate_rows_kernel<T, MM>), dim3(grid), dim3(SG_WARPS * 32), 0, (cudaStream_t)stream, x, ldx, \
+                                           ids, (const T*)side, lds, col0, (const T*)w_gate, (T*)out, ldo, W, n, V, vec_ok));   \
+    break;
+  switch (M) { JL_SG(1) JL_SG(2) JL_SG(3) JL_SG(4) JL_SG(5) JL_SG(6) JL_SG(7) JL_SG(8) }
+#undef JL_SG
   JL_CUDA(cudaGetLastError());
   return JL_OK;
 }

@@ -433,10 +433,10 @@ int jl_embed_pos(const int* ids, const void* table, const void* pos_table, float
 /* out[m, c] = gelu_tanh(t[m, c]) * side[ids[m], col0 + c], c < n; t fp32 (row pitch ldt), side and out of dtype (pitches lds, ldo). */
 int jl_side_gate(const float* t, int ldt, const int* ids, const void* side, int lds, int col0, void* out, int ldo, int M, int n,
                  int V, int dtype, void* stream);
-/* The per-layer token input for a few rows in one launch: y = w_proj (gelu_tanh(w_gate x) * side[ids[m], col0 .. col0 + n));
- * x[m] += y / rms(y) * w_side;  if w_next: h[m] = x[m] / rms(x[m]) * w_next.  x fp32 [M, W]; w_gate [n, W], w_proj [W, n]. */
-int jl_token_side(float* x, const int* ids, const void* side, int lds, int col0, const void* w_gate, const void* w_proj,
-                  const void* w_side, const void* w_next, void* h, int M, int W, int n, int V, float eps, int dtype, void* stream);
+/* The same gate for M <= 8 rows with the small projection inside: out[m, c] = gelu_tanh(w_gate[c, :] . x[m, :]) * side[ids[m], col0 + c];
+ * x fp32 [M, W] (row pitch ldx) is read as it is; w_gate [n, W], side and out of dtype. */
+int jl_side_gate_rows(const float* x, int ldx, const int* ids, const void* side, int lds, int col0, const void* w_gate, void* out,
+                      int ldo, int M, int W, int n, int V, int dtype, void* stream);
 /* jl_attn_prep with: `layout` of the rotated q / k pairs (0: (2i, 2i+1), 1: (i, i + rot/2)); q_norm_w / k_norm_w [D] of dtype, an RMS
  * norm of every head before the rotation (NULL: none); v_cos / v_sin fp32 [v_max_pos][Dv/2]: values rotated at their own position
  * over all Dv channels before they are cached, pairs as v_layout (NULL: cached as they are). */

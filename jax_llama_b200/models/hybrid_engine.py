@@ -85,9 +85,10 @@ class TokenSide:
     """Per-layer token input: y = proj (gelu_tanh(gate x) · Es[token, col0 : col0 + dim]);  x += y / rms(y) · w.  `table` is the
     second embedding table [vocab, layers · dim], shared by the layers; every layer reads its own slice of a row (the same
     slice on every pass of a looped layer).  Many rows: two GEMMs around a small gate kernel, then the fused "norm, add, next
-    norm" step; a few rows (decoding): one launch that keeps the stream row in fp32 throughout."""
+    norm" step; a few rows (decoding): the gate kernel does the small projection itself on the fp32 stream rows, the up
+    projection streams its weights once for all rows."""
 
-    FUSED_ROWS = 8
+    ROWS_KERNEL = 8
 
     def __init__(self, table: torch.Tensor, col0: int, w: Dict[str, torch.Tensor]):
         self.table, self.col0 = table, int(col0)
@@ -99,11 +100,12 @@ class TokenSide:
 
     def run(self, x: torch.Tensor, ids: torch.Tensor, w_next: Optional[torch.Tensor], eps: float) -> Optional[torch.Tensor]:
         """Adds the token input to x (fp32, in place); returns norm(x) · w_next when w_next is given."""
-        if x.shape[0] <= self.FUSED_ROWS:
-            return SK.token_side(x, ids, self.table, self.col0, self.gate, self.proj, self.norm, w_next, eps)
-        xc = x if self.gate.dtype == torch.float32 else SK.act_cast(x, self.gate.dtype)
-        t = SK.linear(xc, self.gate)                                          # fp32 [M, dim]
-        g = SK.side_gate(t, ids, self.table, self.col0, self.dim, self.gate.dtype)
+        if x.shape[0] <= self.ROWS_KERNEL:
+            g = SK.side_gate_rows(x, ids, self.table, self.col0, self.gate)
+        else:
+            xc = x if self.gate.dtype == torch.float32 else SK.act_cast(x, self.gate.dtype)
+            t = SK.linear(xc, self.gate)                                      # fp32 [M, dim]
+            g = SK.side_gate(t, ids, self.table, self.col0, self.dim, self.gate.dtype)
         y = SK.linear(g, self.proj)                                           # fp32 [M, width]
         return SK.postnorm_add(y, self.norm, x, eps, 0.0, w_next=w_next)
 

@@ -622,16 +622,15 @@ def side_gate(t: torch.Tensor, ids: torch.Tensor, side: torch.Tensor, col0: int,
     return out
 
 
-def token_side(x: torch.Tensor, ids: torch.Tensor, side: torch.Tensor, col0: int, w_gate: torch.Tensor, w_proj: torch.Tensor,
-               w_side: torch.Tensor, w_next: Optional[torch.Tensor], eps: float) -> Optional[torch.Tensor]:
-    """One launch for a few rows: y = w_proj (gelu_tanh(w_gate x) · side[ids, col0 : col0 + n]); x += y / rms(y) · w_side in
-    place (fp32); returns x / rms(x) · w_next in the weights' dtype when w_next is given."""
+def side_gate_rows(x: torch.Tensor, ids: torch.Tensor, side: torch.Tensor, col0: int, w_gate: torch.Tensor) -> torch.Tensor:
+    """gelu_tanh(w_gate x[m]) · side[ids[m], col0 : col0 + n] for up to 8 rows in one launch; x fp32 [M, W] is read as it is
+    (not rounded to the weights' type); the result in the weights' dtype."""
     _need(x, torch.float32, "x")
     _need(ids, torch.int32, "ids")
     M, W = x.shape
     n = w_gate.shape[0]
-    h = torch.empty((M, W), dtype=w_next.dtype, device=x.device) if w_next is not None else None
-    _lib.check(_lib.lib().jl_token_side(x.data_ptr(), ids.data_ptr(), side.data_ptr(), side.stride(0), int(col0), w_gate.data_ptr(),
-                                        w_proj.data_ptr(), w_side.data_ptr(), _p(w_next), _p(h), M, W, n, side.shape[0], float(eps),
-                                        dtype_code(w_gate.dtype), _stream()), "jl_token_side")
-    return h
+    out = torch.empty((M, n), dtype=w_gate.dtype, device=x.device)
+    _lib.check(_lib.lib().jl_side_gate_rows(x.data_ptr(), x.stride(0), ids.data_ptr(), side.data_ptr(), side.stride(0), int(col0),
+                                            w_gate.data_ptr(), out.data_ptr(), out.stride(0), M, W, n, side.shape[0],
+                                            dtype_code(w_gate.dtype), _stream()), "jl_side_gate_rows")
+    return out

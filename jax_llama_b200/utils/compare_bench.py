@@ -3,7 +3,8 @@ random weights, plus the time of each kernel of the new design beside the like k
 
 * ``bench.py --compare folirax`` — Folirax beside LLaMA (`run`),
 * ``bench.py --compare nikonex`` — Nikonex beside Folirax (`run_nikonex`),
-* ``bench.py --compare bazulorn`` — Bazulorn beside Nikonex (`run_bazulorn`).
+* ``bench.py --compare bazulorn`` — Bazulorn beside Nikonex (`run_bazulorn`),
+* ``bench.py --compare datozen`` — Datozen beside Bazulorn (`run_datozen`).
 
 Everything is timed with CUDA events on the launching stream after warm-up; per-kernel timings flush L2 (a 256 MB write)
 between iterations, whole-model timings stream more weight bytes than L2 holds.  Fractions are of the measured peaks in
@@ -772,5 +773,235 @@ def run_bazulorn(sizes: List[str], prompt_len: int = 2048, steps: int = 64, warm
             torch.cuda.empty_cache()
         if kernels:
             entry["kernels"] = _bazulorn_kernel_table(s, dev, peaks, prompt_len)
+        result["sizes"][name] = entry
+    return result
+
+
+# --------------------------------------------------------------------------------------------- Datozen beside Bazulorn
+def datozen_config(s: Dict[str, int], positions: int = 4096) -> Any:
+    """Attention layers with 128-wide heads at the head counts of the Nikonex shape, blocks of `window` positions, the same
+    gated experts as the Bazulorn shape (two of the router's outputs are identity experts) behind a dense layer; a quarter of
+    the layer runs come from a stretch that runs twice, so that the number of runs equals the other model's depth."""
+    from ..config import DatozenConfig
+
+    H = s["heads"]
+    att = {"heads": H, "kv_heads": s["kv_heads"], "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": s["window"]},
+           "rot": {"dims": 64, "base": 10000.0, "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}
+    ef, sf = s["expert_ff"] * 2 // 3 // 8 * 8, s["shared_ff"] * 2 // 3 // 8 * 8
+    moe = {"kind": "moe", "expert": {"ff": ef}, "shared": {"ff": sf},
+           "router": {"experts": s["experts"] - 2, "identity": 2, "top": s["top"], "groups": {"count": 4, "keep": 2}}}
+    dense = {"kind": "dense", "ff": s["shared_ff"]}
+    k = max(1, s["layers"] // 4)
+    n = s["layers"] - k
+    layers = [{"type": "attention", "mixer": att, "mlp": dense if i % 4 == 0 else moe} for i in range(n)]
+    return DatozenConfig.from_dict({"architecture": "Datozen", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-5},
+                                    "max_positions": positions, "token_side": {"dim": 256},
+                                    "loop": {"start": n - k, "stop": n, "times": 2}, "layers": layers})
+
+
+def _datozen_kernel_table(s: Dict[str, int], dev: torch.device, peaks: Dict[str, float], prompt_len: int) -> List[Dict[str, Any]]:
+    """Each kernel that Datozen adds or extends, at this size, beside the like kernel of the Bazulorn path: ms, achieved rate,
+    the fraction of the measured roofline, and how much farther from it the new kernel is (`distance_ratio`)."""
+    from ..config import DenseMlpSpec, MoeMlpSpec
+    from ..models.feedforward import DenseFeedForward, MoeFeedForward
+    from ..models.hybrid_engine import TokenSide
+    from ..models.mixers import rotary_table
+    from ..ops import seq_kernels as SK
+
+    t = Timer(dev)
+    hbm, tf = peaks["hbm_gbs"], peaks["bf16_tflops"]
+    W, H, G, V = s["width"], s["heads"], s["kv_heads"], s["vocab"]
+    E, top = s["experts"], s["top"]
+    ef = s["expert_ff"] * 2 // 3 // 8 * 8
+    chunk, P = s["window"], prompt_len
+    D = Dv = 128
+    T = P + 8
+    bf = dict(dtype=torch.bfloat16, device=dev)
+    rows: List[Dict[str, Any]] = []
+
+    def add(name: str, ms: float, like: str, like_ms: float, nbytes: float = 0.0, flops: float = 0.0, like_nbytes: float = 0.0,
+            like_flops: float = 0.0, note: str = "") -> None:
+        r: Dict[str, Any] = {"kernel": name, "ms": round(ms, 4), "like": like, "like_ms": round(like_ms, 4) if like_ms else None}
+        frac = like_frac = None
+        if nbytes:
+            r["gbs"] = round(nbytes / ms / 1e6, 1)
+            frac = nbytes / ms / 1e6 / hbm
+            r["frac_hbm_of_measured"] = round(frac, 4)
+            if like_ms:
+                like_frac = (like_nbytes or nbytes) / like_ms / 1e6 / hbm
+        if flops:
+            r["tflops"] = round(flops / ms / 1e9, 2)
+            frac = flops / ms / 1e9 / tf
+            r["frac_bf16_of_measured"] = round(frac, 5)
+            if like_ms:
+                like_frac = (like_flops or flops) / like_ms / 1e9 / tf
+        if like_frac is not None:
+            r["like_frac"] = round(like_frac, 5)
+            r["distance_ratio"] = round(like_frac / frac, 2)
+        if note:
+            r["note"] = note
+        rows.append(r)
+
+    zero = torch.zeros(1, dtype=torch.int32, device=dev)
+    pad = torch.zeros(1, dtype=torch.int32, device=dev)
+    pad8 = torch.zeros(8, dtype=torch.int32, device=dev)
+    ctx_len = torch.full((1,), P, dtype=torch.int32, device=dev)
+
+    # ---- embedding: token row + position row, beside token row + hashed pair row + norm
+    emb, pair, wn, post = torch.randn(V, W, **bf), torch.randn(65522, W, **bf), torch.ones(W, **bf), torch.randn(T, W, **bf)
+    ids = torch.randint(0, V, (P,), dtype=torch.int32, device=dev)
+    prev = torch.zeros(1, dtype=torch.int32, device=dev)
+    add("embed_pos (token row + position row)", t.kernel(lambda: SK.embed_pos(ids, emb, post, zero, pad, 1, P)),
+        "embed_pair_norm (two table rows, norm; Bazulorn)",
+        t.kernel(lambda: SK.embed_pair_norm(ids, emb, pair, wn, prev, zero, pad, 1, P, 65521, 1000003, 7919, 1e-5)), nbytes=P * W * 8.0)
+
+    # ---- attention, preparation: weighted q / k norms before a half-split rotation, rotated values, append
+    n_qkv = (H + 2 * G) * D
+    yq = torch.randn(P, n_qkv + 8, device=dev) * 0.3
+    bias = torch.zeros(n_qkv + 8, device=dev)
+    qo = torch.empty(P, H * D, **bf)
+    kc, vc = torch.zeros(1, G, T, D, **bf), torch.zeros(1, G, T, Dv, **bf)
+    kc2, vtm = torch.zeros(1, G, T, D, **bf), torch.zeros(1, T, G * Dv, **bf)
+    cos, sin = rotary_table(64, 10000.0, T, dev)
+    vcos, vsin = rotary_table(Dv, 10000.0, T, dev)
+    qw, kw = torch.ones(D, **bf), torch.ones(D, **bf)
+    one = torch.ones(1, 1, device=dev)
+    add("attn_prep (weighted q / k norms, half-split rotation, rotated values, append)",
+        t.kernel(lambda: SK.attn_prep(yq, 0, H * D, (H + G) * D, qo, kc, vc, cos, sin, 64, False, 1e-5, zero, pad, 1, P, H, G, D, Dv,
+                                      layout=SK.ROT_HALF, q_norm_w=qw, k_norm_w=kw, v_cos=vcos, v_sin=vsin)),
+        "attn_prep (biases, unit-RMS values, append; Bazulorn)",
+        t.kernel(lambda: SK.attn_prep(yq, 0, H * D, (H + G) * D, qo, kc2, vtm, one, one, 0, False, 1e-5, zero, pad, 1, P, H, G, D, Dv,
+                                      bias=bias, v_unit_norm=True, v_token_major=True)), nbytes=P * n_qkv * 6.0)
+
+    # ---- attention proper: prompt and one token
+    kc.normal_()
+    vc.normal_()
+    kc2.normal_()
+    vtm.normal_()
+    qf = torch.randn(P, H * D, **bf) * 0.05
+    gate = torch.randn(P, H, device=dev)
+    sink = torch.zeros(H, device=dev)
+    talk = torch.randn(H, H, **bf) * 0.1
+    mixed = torch.empty(P, H * Dv, **bf)
+    blk_keys = sum(i % chunk + 1 for i in range(P))
+    win_keys = sum(min(i + 1, chunk) for i in range(P))
+
+    def attend_mixed(S: int, q: torch.Tensor, length: torch.Tensor, out: torch.Tensor) -> None:
+        per = max(1, 512 // Dv)
+        for c0 in range(0, G, per):
+            gc = min(per, G - c0)
+            o = SK.attn_windowed(q, kc2, vtm[:, :, c0 * Dv:], length, pad, 1, S, H, G, D, gc * Dv, T, D, G * Dv, chunk, D ** -0.5,
+                                 strides=(G * T * D, T * D, T * G * Dv, 0), sink=True, out_f32=True)
+            SK.talk_mix(o, talk, out, H, G, gc, c0, Dv)
+
+    def attend(S: int, q: torch.Tensor, g: torch.Tensor, length: torch.Tensor) -> torch.Tensor:
+        return SK.attn_masked(q, kc, vc, length, pad, 1, S, H, G, D, Dv, D ** -0.5, gate=g, chunk=chunk, sink=True, sink_logit=sink,
+                              v_cos=vcos, v_sin=vsin, v_layout=SK.ROT_HALF)
+
+    add("attention in blocks of positions, learned sink, sums turned back, gate (prompt): attn_rows",
+        t.kernel(lambda: attend(P, qf, gate, zero), reps=3),
+        "attention with a window and mixed head weights (prompt, Bazulorn): attn_rows over all value heads + talk_mix",
+        t.kernel(lambda: attend_mixed(P, qf, zero, mixed), reps=3),
+        flops=2.0 * H * blk_keys * (D + Dv), like_flops=2.0 * H * win_keys * (D + G * Dv),
+        note="the same exact SIMT kernel on both sides; a block hides on average half of what a window of the same size shows")
+    q1, g1 = qf[:1].contiguous(), gate[:1].contiguous()
+    m1 = torch.empty(1, H * Dv, **bf)
+    last = torch.full((1,), P - 1, dtype=torch.int32, device=dev)               # the new token closes a block when chunk divides P
+    seen1 = (P - 1) % chunk + 1
+    add("attention in blocks (one token): attn_split + attn_merge with the turn back and the gate",
+        t.kernel(lambda: attend(1, q1, g1, last)),
+        "attention with a window and mixed head weights (one token, Bazulorn): attn_split + attn_merge + talk_mix",
+        t.kernel(lambda: attend_mixed(1, q1, last, m1)),
+        nbytes=seen1 * G * (D + Dv) * 2.0, like_nbytes=min(chunk, P) * G * (D + Dv) * 2.0,
+        note=f"the new token is position {P - 1}: its block shows {seen1} keys, the window {min(chunk, P)}; both are launch-bound at this length")
+
+    # ---- per-layer token input: prompt (two GEMMs around a gate kernel, fused norm / add / next norm) and 8 rows (one launch)
+    n_side = 256
+    side = TokenSide(torch.randn(V, 4 * n_side, **bf), n_side, {"gate": torch.randn(n_side, W, **bf) * 0.02,
+                                                                 "proj": torch.randn(W, n_side, **bf) * 0.02, "norm": torch.ones(W, **bf)})
+    x = torch.randn(P, W, device=dev)
+    y1, y2 = torch.randn(P, W, device=dev), torch.randn(P, W, device=dev)
+    w1 = torch.ones(W, **bf)
+    add("token input, prompt (cast, gate GEMM, gate kernel, up GEMM, norm + add + next norm)",
+        t.kernel(lambda: side.run(x, ids, w1, 1e-5), reps=5),
+        "branch_add_norm (two branches, two norms; the residual step of every block)",
+        t.kernel(lambda: SK.branch_add_norm(x, y1, y2, 0.5, w1, w1, 1e-5)),
+        nbytes=P * W * (4 + 2 + 4 + 4 + 4 + 2.0) + P * n_side * 8.0, like_nbytes=P * W * 20.0,
+        note="bytes of the five passes; its two products add 4 P W n flops")
+    x8, ids8 = x[:8].contiguous(), ids[:8].contiguous()
+    wl = torch.randn(2 * n_side, W, **bf) * 0.02
+    h8 = torch.randn(8, W, **bf)
+    add("token input, 8 rows (gate kernel with the small projection inside, weight-streaming up projection, norm + add + next norm)",
+        t.kernel(lambda: side.run(x8, ids8, w1, 1e-5)),
+        "weight-streaming linear of the same weight bytes, 8 rows (one launch)", t.kernel(lambda: SK.linear(h8, wl)),
+        nbytes=2.0 * n_side * W * 2, note="three dependent launches of a few microseconds against one")
+
+    # ---- dense feed-forward with the two-parameter activation, beside Bazulorn's gated layer of equal parameters
+    F = s["shared_ff"]
+    hp = torch.randn(P, W, **bf)
+    dn = DenseFeedForward(DenseMlpSpec(ff=F, act="xielu", gated=False),
+                          {"up": torch.randn(F, W, **bf) * 0.02, "down": torch.randn(W, F, **bf) * 0.02, "act": torch.zeros(2, **bf)})
+    Fg = F * 2 // 3 // 8 * 8
+    dg = DenseFeedForward(DenseMlpSpec(ff=Fg, act="gelu_tanh", gated=True),
+                          {"up": torch.randn(Fg, W, **bf) * 0.02, "gate": torch.randn(Fg, W, **bf) * 0.02, "down": torch.randn(W, Fg, **bf) * 0.02})
+    add("dense layer, two-parameter activation (prompt: GEMM, activation in place, GEMM)", t.kernel(lambda: dn.run(hp), reps=5),
+        "gated dense layer (prompt, Bazulorn: GEMM, gated activation, GEMM)", t.kernel(lambda: dg.run(hp), reps=5),
+        flops=4.0 * P * F * W, like_flops=6.0 * P * Fg * W)
+    h1 = hp[:1].contiguous()
+    add("dense layer, one token", t.kernel(lambda: dn.run(h1)), "gated dense layer, one token (Bazulorn)", t.kernel(lambda: dg.run(h1)),
+        nbytes=2.0 * F * W * 2, like_nbytes=3.0 * Fg * W * 2)
+
+    # ---- experts with a choice bias, groups by their best member and identity experts, beside Bazulorn's experts
+    torch.manual_seed(0)
+
+    def make(new: bool) -> MoeFeedForward:
+        n_real = E - 2 if new else E
+        spec = MoeMlpSpec(experts=n_real, top=top, ff=ef, act="silu" if new else "glu_clamped", score="softmax", groups=4 if new else 1,
+                          keep=2 if new else 1, group_top=1, normalise=not new, shared_ff=0, shared_gate=False, gated=True, limit=7.0,
+                          router_bias=not new, identity=2 if new else 0, choice_bias=new)
+        w = {"router": torch.randn(E, W, **bf) * 0.02}
+        w["correction" if new else "router.b"] = torch.zeros(E, **bf)
+        for e in range(n_real):
+            w[f"e{e}.up"], w[f"e{e}.down"] = torch.randn(ef, W, **bf) * 0.02, torch.randn(W, ef, **bf) * 0.02
+            w[f"e{e}.gate"] = torch.randn(ef, W, **bf) * 0.02
+        return MoeFeedForward(spec, w)
+
+    new, old = make(True), make(False)
+    fl = 2.0 * P * top * 3 * ef * W
+    add("experts with identity experts, prompt (router, choice, sort, gather, grouped tcgen05 GEMM, silu gate, grouped GEMM, combine)",
+        t.kernel(lambda: new.run(hp), reps=5), "gated experts, prompt (Bazulorn: the same chain)", t.kernel(lambda: old.run(hp), reps=5),
+        flops=fl * (E - 2) / E, like_flops=fl, note="one pair in sixteen chooses an identity expert and runs no product")
+    add("experts with identity experts, one token", t.kernel(lambda: new.run(h1)), "gated experts, one token (Bazulorn)",
+        t.kernel(lambda: old.run(h1)), nbytes=top * 3.0 * ef * W * 2, note="seven launches against six (the identity weights)")
+    return rows
+
+
+def run_datozen(sizes: List[str], prompt_len: int = 2048, steps: int = 64, warmup: int = 8, batches: List[int] = (1, 8),
+                kernels: bool = True) -> Dict[str, Any]:
+    """Datozen beside the closest existing design, Bazulorn, at equal width, layer runs, head counts and expert sizes."""
+    from ..models.hybrid_engine import HybridEngine
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    root = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    peaks = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+    try:
+        with open(os.path.join(root, "MEASURED_PEAKS.json")) as f:
+            m = json.load(f)
+        peaks = {"hbm_gbs": float(m["hbm_gbs"]), "bf16_tflops": float(m["bf16_tflops"]), "source": "measured"}
+    except (OSError, KeyError, ValueError):
+        pass
+    result: Dict[str, Any] = {"metric": "datozen_vs_bazulorn_equal_size", "data": "synthetic", "dtype": "bf16", "peaks": peaks,
+                              "prompt_len": prompt_len, "steps": steps, "warmup": warmup, "sizes": {}}
+    for name in sizes:
+        s = NIKONEX_SIZES[name]
+        entry: Dict[str, Any] = {"shape": s}
+        for label, cfg in (("datozen", datozen_config(s, positions=prompt_len + steps + warmup + 64)), ("bazulorn", bazulorn_config(s))):
+            eng = HybridEngine.random_init(cfg, dev, seed=0)
+            entry[label] = _model_times(eng, s["vocab"], prompt_len, list(batches), steps, warmup)
+            entry[label]["layer_runs"] = len(eng.runs)
+            del eng
+            torch.cuda.empty_cache()
+        if kernels:
+            entry["kernels"] = _datozen_kernel_table(s, dev, peaks, prompt_len)
         result["sizes"][name] = entry
     return result

@@ -209,9 +209,9 @@ def test_router_with_choice_bias_groups_and_identity_experts(experts, identity, 
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("rows", [1, 5, 8, 9, 70])
-def test_token_input_in_one_launch_and_in_steps(dtype, rows):
-    """The per-layer token input on the stream alone: up to eight rows run one fused launch, more run two products around
-    a gate kernel; both against the oracle, with the norm of the next block formed on the way."""
+def test_token_input_for_few_and_for_many_rows(dtype, rows):
+    """The per-layer token input on the stream alone: up to eight rows run the gate kernel that holds the small projection, more
+    run two products around a gate kernel; both against the oracle, with the norm of the next block formed on the way."""
     from jax_llama_b200.models.hybrid_engine import TokenSide
     V, W, n, layer, L = 30, 56, 6, 2, 4
     g = torch.Generator().manual_seed(rows)
