@@ -3,8 +3,10 @@
 //  * embed_pos_kernel  — token embedding plus a learned position row: x = E[token] + P[position], into the fp32 stream.
 //  * side_gate_kernel  — the gate of a per-layer token input: g = gelu_tanh(t) * Es[token, col0 .. col0 + n), t the fp32
 //    product of a small projection with the stream, Es a second embedding table whose row holds one slice per layer.
-//  * side_gate_rows_kernel — the same gate for a few rows (decoding) with the small projection inside: a warp per gate channel
-//    streams its row of the projection against the fp32 stream rows of all tokens (the stream is not rounded first).
+//  * side_gate_rows_kernel — the same gate for a few rows (decoding) with the small projection inside: a CTA per four gate
+//    channels streams their rows of the projection against the fp32 stream rows of all tokens (the stream is not rounded first).
+//  * branch_add_cast_kernel — the residual step of a block (both branches added to the fp32 stream) with a copy of the updated
+//    stream in the operand type, which the token input's first GEMM reads.
 //
 // Token (b, s) of a call sits at slot *cache_len + s and position slot - pad_left[b]; negative positions are padding.
 #include <stdint.h>
@@ -52,11 +54,12 @@ __global__ void __launch_bounds__(256) side_gate_kernel(const float* __restrict_
   }
 }
 
-constexpr int SG_WARPS = 4, SG_MAXM = 8;
+constexpr int SG_WARPS = 8, SG_CH = 4, SG_MAXM = 8;
 
-// A few rows (decoding): a warp per gate channel c streams row c of the gate projection once (16-byte loads) against the fp32
-// stream rows of all M tokens, then applies gelu_tanh and the token's table entry.  The stream is read as it is (no rounding
-// to the operand type); n / SG_WARPS CTAs share the weight matrix between them.
+// A few rows (decoding): a CTA owns SG_CH gate channels, its warps split the width; a lane reads four elements of every channel's
+// row of the gate projection per step (all loads of a step issued before the first use) against the fp32 stream rows of all M
+// tokens, which are read as they are (no rounding to the operand type).  The warps' sums meet in shared memory in a fixed
+// order; then gelu_tanh and the token's table entry.
 template <typename T, int M>
 __global__ void __launch_bounds__(SG_WARPS * 32) side_gate_rows_kernel(const float* __restrict__ x, int ldx, const int* __restrict__ ids,
                                                                        const T* __restrict__ side, int lds, int col0,
@@ -64,42 +67,93 @@ __global__ void __launch_bounds__(SG_WARPS * 32) side_gate_rows_kernel(const flo
                                                                        int W, int n, int V, int vec_ok) {
   pdl_wait();                      // programmatic dependent launch: nothing is read before the predecessor is done
   pdl_launch_dependents();
+  __shared__ float red[SG_WARPS][SG_CH][M];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int c = blockIdx.x * SG_WARPS + warp;
-  if (c >= n) return;
-  const T* wr = wg + (size_t)c * W;
-  float acc[M];
+  const int c0 = blockIdx.x * SG_CH;
+  float acc[SG_CH][M];
 #pragma unroll
-  for (int m = 0; m < M; ++m) acc[m] = 0.0f;
+  for (int r = 0; r < SG_CH; ++r)
+#pragma unroll
+    for (int m = 0; m < M; ++m) acc[r][m] = 0.0f;
   int done = 0;
   if (vec_ok) {
     const int kv = W / 4 * 4;
-    for (int k = lane * 4; k < kv; k += 128) {
-      float wv[4];
-      load4(wr + k, wv);
+    for (int k = (warp * 32 + lane) * 4; k < kv; k += SG_WARPS * 128) {
+      float wv[SG_CH][4];
+#pragma unroll
+      for (int r = 0; r < SG_CH; ++r) load4(wg + (size_t)min(c0 + r, n - 1) * W + k, wv[r]);
 #pragma unroll
       for (int m = 0; m < M; ++m) {
         float xv[4];
         load4(x + (size_t)m * ldx + k, xv);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) acc[m] = fmaf(wv[j], xv[j], acc[m]);
+        for (int r = 0; r < SG_CH; ++r)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[r][m] = fmaf(wv[r][j], xv[j], acc[r][m]);
       }
     }
     done = kv;
   }
-  for (int k = done + lane; k < W; k += 32) {
-    const float wv = to_f(wr[k]);
+  for (int k = done + warp * 32 + lane; k < W; k += SG_WARPS * 32) {
 #pragma unroll
-    for (int m = 0; m < M; ++m) acc[m] = fmaf(wv, x[(size_t)m * ldx + k], acc[m]);
+    for (int r = 0; r < SG_CH; ++r) {
+      const float wv = to_f(wg[(size_t)min(c0 + r, n - 1) * W + k]);
+#pragma unroll
+      for (int m = 0; m < M; ++m) acc[r][m] = fmaf(wv, x[(size_t)m * ldx + k], acc[r][m]);
+    }
   }
 #pragma unroll
-  for (int m = 0; m < M; ++m) {
-    const float d = warp_sum(acc[m]);
-    if (lane == 0) {
+  for (int r = 0; r < SG_CH; ++r)
+#pragma unroll
+    for (int m = 0; m < M; ++m) {
+      const float d = warp_sum(acc[r][m]);
+      if (lane == 0) red[warp][r][m] = d;
+    }
+  __syncthreads();
+  if (threadIdx.x < SG_CH * M) {
+    const int r = threadIdx.x / M, m = threadIdx.x % M, c = c0 + r;
+    float d = 0.0f;
+#pragma unroll
+    for (int w = 0; w < SG_WARPS; ++w) d += red[w][r][m];
+    if (c < n) {
       int tok = ids[m];
       tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);
       out[(size_t)m * ldo + c] = from_f<T>(apply_act(d, ACT_GELU_TANH, 0.0f, 0.0f) * to_f(side[(size_t)tok * lds + col0 + c]));
     }
+  }
+}
+
+// x[m, :] += mult * (y1[m, :] + y2[m, :]) in place (fp32; either branch may be absent) and a copy of the updated row in the
+// operand type: the residual step of a block whose token input reads the stream itself through a GEMM.
+template <typename T>
+__global__ void __launch_bounds__(256) branch_add_cast_kernel(const float* __restrict__ y1, int ld1, const float* __restrict__ y2,
+                                                              int ld2, float mult, float* __restrict__ x, T* __restrict__ xc, int W,
+                                                              int vec) {
+  pdl_wait();                      // programmatic dependent launch: nothing is read before the predecessor is done
+  pdl_launch_dependents();
+  const size_t m = blockIdx.x;
+  float* xr = x + m * W;
+  const float* a = y1 ? y1 + m * ld1 : nullptr;
+  const float* b = y2 ? y2 + m * ld2 : nullptr;
+  if (vec) {
+    for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {
+      float v[4], s[4] = {0.f, 0.f, 0.f, 0.f}, t[4];
+      load4(xr + i, v);
+      if (a) load4(a + i, s);
+      if (b) { load4(b + i, t);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) s[j] += t[j]; }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[j] = fmaf(mult, s[j], v[j]);
+      store4(xr + i, v);
+      store4(xc + m * W + i, v);
+    }
+    return;
+  }
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float v = fmaf(mult, (a ? a[i] : 0.0f) + (b ? b[i] : 0.0f), xr[i]);
+    xr[i] = v;
+    xc[m * W + i] = from_f<T>(v);
   }
 }
 
@@ -133,7 +187,7 @@ extern "C" JL_API int jl_side_gate_rows(const float* x, int ldx, const int* ids,
   JL_CHECK_ARG(M >= 1 && M <= SG_MAXM && W >= 1 && n >= 1 && V >= 1 && ldx >= W && ldo >= n && col0 >= 0 && lds >= col0 + n,
                "jl_side_gate_rows: bad shape M=%d W=%d n=%d ldx=%d ldo=%d", M, W, n, ldx, ldo);
   const int vec_ok = W % 4 == 0 && ldx % 4 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w_gate % 16 == 0;
-  const dim3 grid((n + SG_WARPS - 1) / SG_WARPS);
+  const dim3 grid((n + SG_CH - 1) / SG_CH);
 #define JL_SG(MM)                                                                                                            \
   case MM:                                                                                                                   \
     JL_DISPATCH_DTYPE(dtype, JL_LAUNCH_PDL((side_gate_rows_kernel<T, MM>), dim3(grid), dim3(SG_WARPS * 32), 0, (cudaStream_t)stream, x, ldx, \
@@ -141,6 +195,18 @@ extern "C" JL_API int jl_side_gate_rows(const float* x, int ldx, const int* ids,
     break;
   switch (M) { JL_SG(1) JL_SG(2) JL_SG(3) JL_SG(4) JL_SG(5) JL_SG(6) JL_SG(7) JL_SG(8) }
 #undef JL_SG
+  JL_CUDA(cudaGetLastError());
+  return JL_OK;
+}
+
+extern "C" JL_API int jl_branch_add_cast(const float* y1, int ld1, const float* y2, int ld2, float mult, float* x, void* xc, int M, int W,
+                                         int dtype, void* stream) {
+  JL_CHECK_ARG(M >= 1 && W >= 1 && xc != nullptr, "jl_branch_add_cast: bad shape M=%d W=%d", M, W);
+  JL_CHECK_ARG((y1 == nullptr || ld1 >= W) && (y2 == nullptr || ld2 >= W), "jl_branch_add_cast: row pitch below W=%d", W);
+  const int vec = W % 4 == 0 && (y1 == nullptr || ld1 % 4 == 0) && (y2 == nullptr || ld2 % 4 == 0) && (uintptr_t)y1 % 16 == 0 &&
+                  (uintptr_t)y2 % 16 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)xc % 16 == 0;
+  JL_DISPATCH_DTYPE(dtype, JL_LAUNCH_PDL(branch_add_cast_kernel<T>, dim3(M), dim3(256), 0, (cudaStream_t)stream, y1, ld1, y2, ld2, mult, x,
+                                         (T*)xc, W, vec));
   JL_CUDA(cudaGetLastError());
   return JL_OK;
 }

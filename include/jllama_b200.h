@@ -437,6 +437,9 @@ int jl_side_gate(const float* t, int ldt, const int* ids, const void* side, int 
  * x fp32 [M, W] (row pitch ldx) is read as it is; w_gate [n, W], side and out of dtype. */
 int jl_side_gate_rows(const float* x, int ldx, const int* ids, const void* side, int lds, int col0, const void* w_gate, void* out,
                       int ldo, int M, int W, int n, int V, int dtype, void* stream);
+/* x[m] += mult * (y1[m] + y2[m]) in place (fp32 [M, W]; either branch may be NULL) and xc[m] = the updated row in dtype. */
+int jl_branch_add_cast(const float* y1, int ld1, const float* y2, int ld2, float mult, float* x, void* xc, int M, int W, int dtype,
+                       void* stream);
 /* jl_attn_prep with: `layout` of the rotated q / k pairs (0: (2i, 2i+1), 1: (i, i + rot/2)); q_norm_w / k_norm_w [D] of dtype, an RMS
  * norm of every head before the rotation (NULL: none); v_cos / v_sin fp32 [v_max_pos][Dv/2]: values rotated at their own position
  * over all Dv channels before they are cached, pairs as v_layout (NULL: cached as they are). */

@@ -98,12 +98,18 @@ class TokenSide:
     def weights(self) -> List[torch.Tensor]:
         return [self.gate, self.proj, self.norm]
 
-    def run(self, x: torch.Tensor, ids: torch.Tensor, w_next: Optional[torch.Tensor], eps: float) -> Optional[torch.Tensor]:
-        """Adds the token input to x (fp32, in place); returns norm(x) · w_next when w_next is given."""
+    def wants_cast(self, rows: int) -> bool:
+        """Whether `run` reads a copy of the stream in the operand type (the caller's residual step can write it on the way)."""
+        return rows > self.ROWS_KERNEL and self.gate.dtype != torch.float32
+
+    def run(self, x: torch.Tensor, ids: torch.Tensor, w_next: Optional[torch.Tensor], eps: float,
+            x_cast: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+        """Adds the token input to x (fp32, in place); returns norm(x) · w_next when w_next is given.  x_cast: x in the operand
+        type, when the caller has it."""
         if x.shape[0] <= self.ROWS_KERNEL:
             g = SK.side_gate_rows(x, ids, self.table, self.col0, self.gate)
         else:
-            xc = x if self.gate.dtype == torch.float32 else SK.act_cast(x, self.gate.dtype)
+            xc = x_cast if x_cast is not None else (x if self.gate.dtype == torch.float32 else SK.act_cast(x, self.gate.dtype))
             t = SK.linear(xc, self.gate)                                      # fp32 [M, dim]
             g = SK.side_gate(t, ids, self.table, self.col0, self.dim, self.gate.dtype)
         y = SK.linear(g, self.proj)                                           # fp32 [M, width]
@@ -437,8 +443,12 @@ class HybridEngine(B200Engine):
                 h1, h2 = SK.branch_add_norm(x, y1, y2, mult, w1, w2, eps)
             else:
                 # the token input reads the stream after both branches were added, and forms the next block's norm itself
-                SK.branch_add_norm(x, y1, y2, mult, None, None, eps)
-                h1 = l.side.run(x, cache.step_ids, w1 if self.shared_norm else None, eps)
+                xc = None
+                if l.side.wants_cast(B * S):
+                    xc = SK.branch_add_cast(x, y1, y2, mult, self.dtype)
+                else:
+                    SK.branch_add_norm(x, y1, y2, mult, None, None, eps)
+                h1 = l.side.run(x, cache.step_ids, w1 if self.shared_norm else None, eps, x_cast=xc)
                 if not self.shared_norm and nxt is not None:
                     h1, h2 = SK.branch_add_norm(x, None, None, mult, w1, w2, eps)
             if self.capture_streams is not None:

@@ -93,6 +93,7 @@ _HYBRID = {
     "jl_delta_scan_ws_floats": (sz, [i32] * 5),
     "jl_embed_pos": (i32, [ip, vp, vp, fp, ip, ip] + [i32] * 6 + [vp]),
     "jl_side_gate": (i32, [fp, i32, ip, vp, i32, i32, vp, i32, i32, i32, i32, i32, vp]),
+    "jl_branch_add_cast": (i32, [fp, i32, fp, i32, f32, fp, vp, i32, i32, i32, vp]),
     "jl_side_gate_rows": (i32, [fp, i32, ip, vp, i32, i32, vp, vp, i32, i32, i32, i32, i32, i32, vp]),
     "jl_attn_prep_ex": (i32, [fp, i32, i32, i32, i32, vp, vp, vp, fp, fp, i32, i32, i32, i32, vp, vp, f32, fp, fp, i32, i32, ip, ip]
                         + [i32] * 7 + [fp, i32, i32, i32, vp]),

@@ -634,3 +634,15 @@ def side_gate_rows(x: torch.Tensor, ids: torch.Tensor, side: torch.Tensor, col0:
                                             w_gate.data_ptr(), out.data_ptr(), out.stride(0), M, W, n, side.shape[0],
                                             dtype_code(w_gate.dtype), _stream()), "jl_side_gate_rows")
     return out
+
+
+def branch_add_cast(x: torch.Tensor, y1: Optional[torch.Tensor], y2: Optional[torch.Tensor], mult: float, dtype: torch.dtype
+                    ) -> torch.Tensor:
+    """x += mult · (y1 + y2) in place (fp32; either branch may be None); returns the updated rows in `dtype`."""
+    _need(x, torch.float32, "x")
+    M, W = x.shape
+    xc = torch.empty((M, W), dtype=dtype, device=x.device)
+    _lib.check(_lib.lib().jl_branch_add_cast(_p(y1), y1.stride(0) if y1 is not None else 0, _p(y2),
+                                             y2.stride(0) if y2 is not None else 0, float(mult), x.data_ptr(), xc.data_ptr(), M, W,
+                                             dtype_code(dtype), _stream()), "jl_branch_add_cast")
+    return xc

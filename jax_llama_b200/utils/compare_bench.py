@@ -922,12 +922,14 @@ def _datozen_kernel_table(s: Dict[str, int], dev: torch.device, peaks: Dict[str,
     x = torch.randn(P, W, device=dev)
     y1, y2 = torch.randn(P, W, device=dev), torch.randn(P, W, device=dev)
     w1 = torch.ones(W, **bf)
-    add("token input, prompt (cast, gate GEMM, gate kernel, up GEMM, norm + add + next norm)",
-        t.kernel(lambda: side.run(x, ids, w1, 1e-5), reps=5),
-        "branch_add_norm (two branches, two norms; the residual step of every block)",
+    def block_end() -> None:
+        side.run(x, ids, w1, 1e-5, x_cast=SK.branch_add_cast(x, y1, y2, 1.0, torch.bfloat16))
+
+    add("residual step + token input, prompt (add + cast, gate GEMM, gate kernel, up GEMM, norm + add + next norm)",
+        t.kernel(block_end, reps=5), "branch_add_norm (two branches, two norms; the residual step of every block)",
         t.kernel(lambda: SK.branch_add_norm(x, y1, y2, 0.5, w1, w1, 1e-5)),
-        nbytes=P * W * (4 + 2 + 4 + 4 + 4 + 2.0) + P * n_side * 8.0, like_nbytes=P * W * 20.0,
-        note="bytes of the five passes; its two products add 4 P W n flops")
+        nbytes=P * W * (18 + 2 + 4 + 14.0) + P * n_side * 8.0, like_nbytes=P * W * 20.0,
+        note="bytes of the five passes (the residual step among them); its two products add 4 P W n flops")
     x8, ids8 = x[:8].contiguous(), ids[:8].contiguous()
     wl = torch.randn(2 * n_side, W, **bf) * 0.02
     h8 = torch.randn(8, W, **bf)
