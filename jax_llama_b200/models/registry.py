@@ -63,7 +63,7 @@ register("llama", LLaMAConfig, _llama)
 register("folirax", FoliraxConfig, _folirax, kernel_subset="hybrid", dtypes=("bfloat16", "float32"))
 register("nikonex", NikonexConfig, _nikonex, kernel_subset="hybrid", dtypes=("bfloat16", "float32"))
 register("bazulorn", BazulornConfig, _bazulorn, kernel_subset="hybrid", dtypes=("bfloat16", "float32"))
-register("datozen", DatozenConfig, _datozen, kernel_subset="hybrid", dtypes=("bfloat16", "float32"))
+register("datozen", DatozenConfig, _datozen, kernel_subset="hybrid_attention", dtypes=("bfloat16", "float32"))
 
 
 def architecture_of(config: Dict[str, Any]) -> str:

@@ -50,7 +50,10 @@ def test_config_round_trip(tmp_path):
     again = DatozenConfig.from_pretrained(str(tmp_path))
     assert again.to_dict() == c.to_dict()
     assert registry.resolve(str(tmp_path))[:2] == ("datozen", DatozenConfig)
-    assert registry.kernel_subset("datozen") == "hybrid" and "float32" in registry.gpu_dtypes("datozen")
+    from jax_llama_b200.ops.build import SUBSETS
+    sub = registry.kernel_subset("datozen")
+    assert "float32" in registry.gpu_dtypes("datozen") and set(SUBSETS[sub]) < set(SUBSETS["hybrid"])
+    assert "seq_token.cu" in SUBSETS[sub] and not {"gla_scan.cu", "delta_scan.cu", "flash_prefill.cu"} & set(SUBSETS[sub])
 
 
 def test_layer_runs_and_defaults():
