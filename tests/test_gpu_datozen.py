@@ -242,6 +242,9 @@ SINGLE = {
     "attention_and_experts": [att(mlp=moe())],
     "experts_without_extras": [att(mlp=moe(experts=5, top=2, identity=0, groups=None, shared=0))],
     "one_group_kept": [att(mlp=moe(experts=9, top=2, identity=3, groups=(4, 1), shared=8))],
+    "seventeen_query_heads_per_value_head": [att(heads=34, kv_heads=2, dim=8, vdim=8, chunk=50, rot=4)],
+    "value_rows_of_320_channels": [att(heads=2, kv_heads=1, dim=16, vdim=320, chunk=40, rot=16)],
+    "keys_of_264_channels": [att(heads=2, kv_heads=2, dim=264, vdim=8, chunk=0, rot=100, scale=0.06)],
 }
 
 
@@ -251,8 +254,16 @@ def test_single_mechanism_models(dtype, name):
     cfg = config(SINGLE[name], side=0 if "unrotated" in name else 6, dtype=dtype)
     eng, cpu = build(cfg, dtype, seed=3)
     toks = tokens(75, cfg.vocab_size, 9)
+    want = oracle_logits(cfg, cpu, toks)
     got = eng.forward(torch.tensor([toks], device="cuda")).logits[0]
-    assert err(got, oracle_logits(cfg, cpu, toks)) < tol(dtype, cfg)
+    assert err(got, want) < tol(dtype, cfg)
+    stream = eng.begin_stream(torch.tensor([toks[:70]], device="cuda"), None, max_length=80, eos_token_id=-1)
+    rows = []
+    for t in toks[70:]:
+        stream.step(feed([t]))
+        rows.append(stream.logits()[0].clone())
+    stream.close()
+    assert err(torch.stack(rows), want[70:]) < tol(dtype, cfg)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
