@@ -34,6 +34,13 @@ struct FlashParams {
   const int* pad_left;
   int B, S, nh, nkv, T, start;
   float scale_log2;
+  // what the v2 kernel takes besides plain causal attention (all off when zero / null):
+  int chunk;                        // > 0: positions (slot - pad_left) form blocks of `chunk`; a query sees the keys of its own block only
+  int sink;                         // the softmax denominator has one more term exp(sink_logit[h]) (exp(0) without logits)
+  const float* sink_logit;          // fp32 [nh] or nullptr
+  const float* gate; int ldg;       // fp32 pre-activation of a sigmoid per (token, head) on the output (column h of row m), or nullptr
+  const float* vcos; const float* vsin; int v_max_pos;   // [v_max_pos][64]: the cached values were rotated at their own positions over
+                                    // all 128 channels (pairs m, m + 64); every row of the output is rotated back by its position
 };
 
 __device__ __forceinline__ void fence_proxy_async() {
@@ -258,7 +265,9 @@ constexpr float F2_RESCALE_THRESHOLD = 8.0f;                 // log2 units
 // P_TMEM: the probabilities go back to the tensor core through TMEM (tcgen05.st over the columns of the
 // score tile they were computed from; A operand of P·V read from TMEM) instead of swizzled shared memory:
 // no generic→async proxy fence, and the softmax warps no longer wait for P·V_{j-1} before producing P_j.
-template <bool P_TMEM>
+// MASKED: the kernel also reads the block size, sink, gate and value-rotation fields of its parameters (one more instance, so that
+// plain causal attention keeps its register budget).
+template <bool P_TMEM, bool MASKED = false>
 __global__ void __launch_bounds__(256, 2)   // 256: caps registers at 128 so that two 6-warp CTAs (allocated as 8) fit
 flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                      const __grid_constant__ CUtensorMap tmap_v, const FlashParams p) {
@@ -310,7 +319,9 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
 
   const int pad = p.pad_left ? p.pad_left[b] : 0;
   const int q_hi = min(q0 + FA_BM, p.S) - 1;
-  const int first_tile = pad / F2_BN;
+  int lo_cta = pad;                                        // first key any query of this tile sees (its first query's)
+  if (MASKED && p.chunk > 0 && p.start + q0 >= pad) lo_cta = pad + (p.start + q0 - pad) / p.chunk * p.chunk;
+  const int first_tile = lo_cta / F2_BN;
   const int last_tile = (p.start + q_hi) / F2_BN;
   const int n_tiles = last_tile - first_tile + 1 > 0 ? last_tile - first_tile + 1 : 0;
 
@@ -387,10 +398,17 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
     float m_ref = -INFINITY, l_run = 0.f;
     const uint32_t p_row = sP + r * 128;
+    // first key this row sees, and the same for the warp's last row (the largest of the warp: bounds grow with the slot)
+    int lo_row = pad, lo_warp = pad;
+    if (MASKED && p.chunk > 0) {
+      const int q_last = p.start + q0 + quarter * 32 + 31;
+      if (q_slot >= pad) lo_row = pad + (q_slot - pad) / p.chunk * p.chunk;
+      if (q_last >= pad) lo_warp = pad + (q_last - pad) / p.chunk * p.chunk;
+    }
 
     for (int j = 0; j < n_tiles; ++j) {
       const int key0 = (first_tile + j) * F2_BN;
-      const bool need_mask = (key0 + F2_BN - 1 > p.start + q0 + quarter * 32) || (key0 < pad);   // warp-uniform
+      const bool need_mask = (key0 + F2_BN - 1 > p.start + q0 + quarter * 32) || (key0 < lo_warp);   // warp-uniform
       tc::mbar_wait(s_full(j & 1), (j >> 1) & 1);
       tc::fence_after_sync();
       uint32_t v0[32], v1[32];
@@ -400,8 +418,8 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       if (need_mask) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          if (key0 + i > q_slot || key0 + i < pad) v0[i] = 0xff800000u;             // -inf
-          if (key0 + 32 + i > q_slot || key0 + 32 + i < pad) v1[i] = 0xff800000u;
+          if (key0 + i > q_slot || key0 + i < lo_row) v0[i] = 0xff800000u;             // -inf
+          if (key0 + 32 + i > q_slot || key0 + 32 + i < lo_row) v1[i] = 0xff800000u;
         }
       }
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -490,8 +508,55 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
       tc::mbar_wait(o_full, (n_tiles - 1) & 1);
       tc::fence_after_sync();
     }
-    const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+    float inv = 0.f;
+    if (l_run > 0.f) {                                       // m_ref is finite here; the sink's share is exp(logit) against the same reference
+      const float extra = (MASKED && p.sink) ? exp2f((p.sink_logit ? p.sink_logit[h] : 0.f) * 1.4426950408889634f - m_ref) : 0.f;
+      inv = 1.0f / (l_run + extra);
+    }
     uint4* dst = reinterpret_cast<uint4*>(p.out + ((size_t)(b * p.S + q0 + r) * p.nh + h) * FA_HD);
+    const bool row_on = q0 + r < p.S;
+    if (MASKED && p.gate != nullptr && row_on) inv *= 1.0f / (1.0f + __expf(-p.gate[(size_t)(b * p.S + q0 + r) * p.ldg + h]));
+    if (MASKED && p.vcos != nullptr) {
+      // the row's sum is turned back by its position: channel m pairs with m + 64, so column chunks 0 / 1 meet chunks 2 / 3
+      int pos = q_slot - pad;
+      pos = pos < 0 ? 0 : (pos >= p.v_max_pos ? p.v_max_pos - 1 : pos);
+      const float* ct = p.vcos + (size_t)pos * 64;
+      const float* st = p.vsin + (size_t)pos * 64;
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        uint32_t oa[32], ob[32];
+        if (n_tiles > 0) {
+          tc::tmem_ld32(tO + lane_off + c * 32, oa);
+          tc::tmem_ld32(tO + lane_off + (c + 2) * 32, ob);
+          tc::tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) oa[i] = ob[i] = 0u;
+        }
+        if (row_on) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float u = __uint_as_float(oa[i]) * inv, v = __uint_as_float(ob[i]) * inv;
+            const float cs = ct[c * 32 + i], sn = st[c * 32 + i];
+            oa[i] = __float_as_uint(u * cs + v * sn);                 // the turn by -position
+            ob[i] = __float_as_uint(v * cs - u * sn);
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            dst[c * 4 + i] = make_uint4(
+                pack_bf16(__uint_as_float(oa[8 * i]), __uint_as_float(oa[8 * i + 1])),
+                pack_bf16(__uint_as_float(oa[8 * i + 2]), __uint_as_float(oa[8 * i + 3])),
+                pack_bf16(__uint_as_float(oa[8 * i + 4]), __uint_as_float(oa[8 * i + 5])),
+                pack_bf16(__uint_as_float(oa[8 * i + 6]), __uint_as_float(oa[8 * i + 7])));
+            dst[(c + 2) * 4 + i] = make_uint4(
+                pack_bf16(__uint_as_float(ob[8 * i]), __uint_as_float(ob[8 * i + 1])),
+                pack_bf16(__uint_as_float(ob[8 * i + 2]), __uint_as_float(ob[8 * i + 3])),
+                pack_bf16(__uint_as_float(ob[8 * i + 4]), __uint_as_float(ob[8 * i + 5])),
+                pack_bf16(__uint_as_float(ob[8 * i + 6]), __uint_as_float(ob[8 * i + 7])));
+          }
+        }
+      }
+    } else {
 #pragma unroll 1
     for (int c = 0; c < 4; ++c) {
       uint32_t o[32];
@@ -511,6 +576,7 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
               pack_bf16(__uint_as_float(o[8 * i + 4]) * inv, __uint_as_float(o[8 * i + 5]) * inv),
               pack_bf16(__uint_as_float(o[8 * i + 6]) * inv, __uint_as_float(o[8 * i + 7]) * inv));
       }
+    }
     }
     tc::fence_before_sync();
   }
@@ -545,20 +611,47 @@ extern "C" JL_API int jl_flash_prefill_occupancy(int smem_override) {
   return n;
 }
 
+static int flash_launch(const void* q, const void* k_cache, const void* v_cache, const int* pad_left, void* out, int B, int S, int nh,
+                        int nkv, int hd, int T, int start, float scale, void* stream, int chunk, int sink, const float* sink_logit,
+                        const float* gate, int ldg, const float* vcos, const float* vsin, int v_max_pos);
+
 extern "C" JL_API int jl_flash_prefill(const void* q, const void* k_cache, const void* v_cache,
                                        const int* cache_len_ptr, const int* pad_left, void* out, int B, int S,
                                        int nh, int nkv, int hd, int T, int start, float scale, void* stream) {
   (void)cache_len_ptr;
+  return flash_launch(q, k_cache, v_cache, pad_left, out, B, S, nh, nkv, hd, T, start, scale, stream, 0, 0, nullptr, nullptr, 0, nullptr,
+                      nullptr, 0);
+}
+
+// The tcgen05 kernel (128-wide heads) with blocks of `chunk` positions, a sink in the denominator (logit per head), a sigmoid gate
+// per (token, head) and the turn back of values that were cached rotated at their own positions (pairs m, m + 64).
+extern "C" JL_API int jl_flash_prefill_masked(const void* q, const void* k_cache, const void* v_cache, const int* pad_left, void* out,
+                                              int B, int S, int nh, int nkv, int hd, int T, int start, float scale, int chunk,
+                                              int sink, const float* sink_logit, const float* gate, int ldg, const float* v_cos,
+                                              const float* v_sin, int v_max_pos, void* stream) {
+  JL_CHECK_ARG(hd == FA_HD, "jl_flash_prefill_masked: head_dim=%d (128 is built)", hd);
+  JL_CHECK_ARG(chunk >= 0 && (sink_logit == nullptr || sink) && (gate == nullptr || ldg >= nh),
+               "jl_flash_prefill_masked: chunk %d, sink %d, gate pitch %d", chunk, sink, ldg);
+  JL_CHECK_ARG(v_cos == nullptr || (v_sin != nullptr && v_max_pos >= 1), "jl_flash_prefill_masked: rotated values need both tables");
+  return flash_launch(q, k_cache, v_cache, pad_left, out, B, S, nh, nkv, hd, T, start, scale, stream, chunk, sink, sink_logit, gate, ldg,
+                      v_cos, v_sin, v_max_pos);
+}
+
+static int flash_launch(const void* q, const void* k_cache, const void* v_cache, const int* pad_left, void* out, int B, int S, int nh,
+                        int nkv, int hd, int T, int start, float scale, void* stream, int chunk, int sink, const float* sink_logit,
+                        const float* gate, int ldg, const float* vcos, const float* vsin, int v_max_pos) {
+  const bool extras = chunk > 0 || sink || gate != nullptr || vcos != nullptr;
   // 64-wide heads (1B-class LLaMA-architecture models) go to the warp-level tensor-core kernel (prefill_attn_mma.cu);
   // JLLAMA_PREFILL_MMA=1 sends head_dim 128 there too (A/B against the tcgen05 kernel below)
   static const bool force_mma = [] { const char* e = getenv("JLLAMA_PREFILL_MMA"); return e && e[0] == '1'; }();
-  if (hd == 64 || (force_mma && hd == 128))
+  if (!extras && (hd == 64 || (force_mma && hd == 128)))
     return jl_prefill_attn_mma(q, k_cache, v_cache, pad_left, out, B, S, nh, nkv, hd, T, start, scale, stream);
   JL_CHECK_ARG(hd == FA_HD, "jl_flash_prefill: head_dim=%d (64 and 128 are built)", hd);
   JL_CHECK_ARG(nkv > 0 && nh % nkv == 0, "jl_flash_prefill: nh=%d not a multiple of nkv=%d", nh, nkv);
   JL_CHECK_ARG(start >= 0 && start + S <= T, "jl_flash_prefill: start=%d + S=%d exceeds cache capacity %d", start, S, T);
   if (B * S == 0) return JL_OK;
-  static const bool use_v1 = [] { const char* e = getenv("JLLAMA_FLASH_V1"); return e && e[0] == '1'; }();
+  static const bool env_v1 = [] { const char* e = getenv("JLLAMA_FLASH_V1"); return e && e[0] == '1'; }();
+  const bool use_v1 = env_v1 && !extras;                   // the first version knows plain causal attention only
   const int bn = use_v1 ? FA_BN : F2_BN;
   CUtensorMap tq, tk, tv;
   int rc = make_tmap_2d_bf16(&tq, q, (uint64_t)B * S, (uint64_t)nh * hd, (uint64_t)nh * hd, FA_BM);
@@ -567,7 +660,8 @@ extern "C" JL_API int jl_flash_prefill(const void* q, const void* k_cache, const
   if (rc) return rc;
   rc = make_tmap_3d_bf16(&tv, v_cache, (uint64_t)B * nkv, T, hd, (uint64_t)T * hd, hd, bn);
   if (rc) return rc;
-  FlashParams p{(__nv_bfloat16*)out, pad_left, B, S, nh, nkv, T, start, scale * 1.4426950408889634f};
+  FlashParams p{(__nv_bfloat16*)out, pad_left, B, S, nh, nkv, T, start, scale * 1.4426950408889634f,
+                chunk, sink, sink_logit, gate, ldg, vcos, vsin, v_max_pos};
   dim3 grid((S + FA_BM - 1) / FA_BM, nh, B);
   if (use_v1) {
     const size_t smem = 6 * FA_TILE_BYTES + 128 + 1024;
@@ -576,9 +670,15 @@ extern "C" JL_API int jl_flash_prefill(const void* q, const void* k_cache, const
     return JL_OK;
   }
   static const bool p_smem = [] { const char* e = getenv("JLLAMA_FLASH_PSMEM"); return e && e[0] == '1'; }();
-  if (p_smem) {
+  if (p_smem && !extras) {
     JL_CUDA(cudaFuncSetAttribute(flash_prefill_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)f2_smem_bytes(false)));
     JL_CUDA(launch_pdl(flash_prefill_kernel<false>, grid, dim3(F2_THREADS), f2_smem_bytes(false), (cudaStream_t)stream, tq, tk, tv, p));
+    return JL_OK;
+  }
+  if (extras) {
+    JL_CUDA(cudaFuncSetAttribute(flash_prefill_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)f2_smem_bytes(true)));
+    JL_CUDA(cudaFuncSetAttribute(flash_prefill_kernel<true, true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+    JL_CUDA(launch_pdl(flash_prefill_kernel<true, true>, grid, dim3(F2_THREADS), f2_smem_bytes(true), (cudaStream_t)stream, tq, tk, tv, p));
     return JL_OK;
   }
   JL_CUDA(cudaFuncSetAttribute(flash_prefill_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)f2_smem_bytes(true)));

@@ -457,6 +457,13 @@ int jl_attn_masked(const void* q, const void* k_cache, const void* v_cache, void
                    long long k_bs, long long k_hs, long long v_bs, long long v_hs, int window, int chunk, float scale, float* scratch,
                    int splits, int sink, const float* sink_logit, const float* v_cos, const float* v_sin, int v_max_pos,
                    int v_layout, float* out32, int dtype, void* stream);
+/* The tcgen05 prompt attention kernel (bfloat16, 128-wide heads; caches [B, nkv, T, 128]) with blocks of `chunk` positions, a sink in
+ * the denominator (sink_logit fp32 [nh] or NULL for exp(0)), a sigmoid gate per (token, head) (fp32 pre-activation, pitch ldg) and the
+ * turn back of values cached rotated at their own positions (v_cos / v_sin fp32 [v_max_pos][64], pairs m, m + 64).  `start`: slots
+ * filled before this call's S tokens per row. */
+int jl_flash_prefill_masked(const void* q, const void* k_cache, const void* v_cache, const int* pad_left, void* out, int B, int S,
+                            int nh, int nkv, int hd, int T, int start, float scale, int chunk, int sink, const float* sink_logit,
+                            const float* gate, int ldg, const float* v_cos, const float* v_sin, int v_max_pos, void* stream);
 /* jl_moe_route with: choice_bias fp32 [E] added to the scores for the choice (group scores and top) only; experts n_real .. E-1
  * are identity experts: a chosen one is reported as expert -1 (jl_moe_sort and the grouped linears skip it) and its weight is
  * added to ident_w[m]. */

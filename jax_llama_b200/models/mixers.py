@@ -196,6 +196,16 @@ class AttentionMixer(Mixer):
             return self._attend_mixed(q, kc, vc, cache, B, S)
         gate = y[:, self.g_off:self.g_off + s.heads] if s.head_gate else None
         if not self.plain and (gate is not None or s.chunk or s.sink_learned or s.v_rot):
+            if S > 1 and self._flash_masked_shape():
+                # prompts of 128-wide heads in bfloat16: the tcgen05 kernel with the block bound, the sink, the gate and the turn
+                # back in its softmax and epilogue
+                out = torch.empty((B * S, s.heads * s.vdim), dtype=self.dtype, device=q.device)
+                _lib.check(_lib.lib().jl_flash_prefill_masked(
+                    q.data_ptr(), kc.data_ptr(), vc.data_ptr(), cache.pad_left.data_ptr(), out.data_ptr(), B, S, s.heads,
+                    s.kv_heads, s.dim, kc.shape[2], int(cache.index), float(s.scale), int(s.chunk), int(s.sink),
+                    K._p(self.sink_logit), K._p(gate), gate.stride(0) if gate is not None else 0, K._p(v_cos), K._p(v_sin),
+                    v_cos.shape[0] if v_cos is not None else 0, K._stream()), "jl_flash_prefill_masked")
+                return out
             return SK.attn_masked(q, kc, vc, cache.len_dev, cache.pad_left, B, S, s.heads, s.kv_heads, s.dim, s.vdim, s.scale,
                                   gate=gate, window=s.window, chunk=s.chunk, sink=s.sink, sink_logit=self.sink_logit,
                                   v_cos=v_cos, v_sin=v_sin, v_layout=layout)
@@ -230,6 +240,14 @@ class AttentionMixer(Mixer):
                                  s.window, s.scale, strides=(G * T * s.dim, T * s.dim, T * row, 0), sink=s.sink, out_f32=True)
             SK.talk_mix(o, self.talk, out, H, G, gc, c0, s.vdim)
         return out
+
+    def _flash_masked_shape(self) -> bool:
+        """Whether prompts can run the tcgen05 kernel in its masked form: bfloat16, 128-wide keys and values, a layer's own
+        head-major caches, no window, values rotated in the half-split pairing (or not at all)."""
+        s = self.spec
+        return (SK.tensor_cores_enabled() and self.dtype == torch.bfloat16 and s.dim == s.vdim == 128 and not self.shares_kv
+                and s.heads // s.kv_heads in (1, 2, 4, 8, 16) and not (s.window or s.bias or s.v_unit_norm or s.talking_heads)
+                and (not s.v_rot or s.rot.layout == "half") and _lib.has("jl_flash_prefill_masked"))
 
     def _library_shape(self) -> bool:
         s = self.spec

@@ -108,6 +108,7 @@ _OPTIONAL = {
     "jl_flash_prefill_occupancy": (i32, [i32]),
     "jl_decode_mega_stages": (i32, [i32, i32, i32, i32, i32, i32]),
     "jl_flash_prefill": (i32, [vp, vp, vp, ip, ip, vp, i32, i32, i32, i32, i32, i32, i32, f32, vp]),
+    "jl_flash_prefill_masked": (i32, [vp, vp, vp, ip, vp] + [i32] * 7 + [f32, i32, i32, fp, fp, i32, fp, fp, i32, vp]),
     "jl_prefill_attn_mma": (i32, [vp, vp, vp, ip, vp, i32, i32, i32, i32, i32, i32, i32, f32, vp]),
 }
 

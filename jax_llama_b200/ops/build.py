@@ -33,10 +33,11 @@ PRECISE_SOURCES = {"seq_norm.cu", "seq_linear.cu", "attn_generic.cu", "gla_scan.
 SUBSETS = {
     "hybrid": ["error.cu", "seq_norm.cu", "seq_linear.cu", "attn_generic.cu", "gla_scan.cu", "moe.cu", "seq_mix.cu", "delta_scan.cu", "seq_token.cu", "sample_full.cu",
                "gemm_tcgen05.cu", "gemm_2cta.cu", "tensormap.cu", "flash_prefill.cu", "prefill_attn_mma.cu", "decode_attn.cu"],
-    # the members of the hybrid family whose only mixer is the generic softmax attention: no recurrent scans and none of the
-    # fixed-head-size attention kernels
+    # the members of the hybrid family whose only mixer is softmax attention: no recurrent scans, no one-token kernel of the
+    # fixed head sizes
     "hybrid_attention": ["error.cu", "seq_norm.cu", "seq_linear.cu", "attn_generic.cu", "moe.cu", "seq_mix.cu", "seq_token.cu",
-                         "sample_full.cu", "gemm_tcgen05.cu", "gemm_2cta.cu", "tensormap.cu"],
+                         "sample_full.cu", "gemm_tcgen05.cu", "gemm_2cta.cu", "tensormap.cu", "flash_prefill.cu",
+                         "prefill_attn_mma.cu"],
 }
 
 

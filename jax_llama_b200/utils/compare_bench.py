@@ -904,6 +904,23 @@ def _datozen_kernel_table(s: Dict[str, int], dev: torch.device, peaks: Dict[str,
         t.kernel(lambda: attend_mixed(P, qf, zero, mixed), reps=3),
         flops=2.0 * H * blk_keys * (D + Dv), like_flops=2.0 * H * win_keys * (D + G * Dv),
         note="the same exact SIMT kernel on both sides; a block hides on average half of what a window of the same size shows")
+    from ..ops import _lib as L
+    from ..ops import kernels as K
+    fo = torch.empty(P, H * Dv, **bf)
+
+    def flash(masked: bool) -> None:
+        if masked:
+            L.check(L.lib().jl_flash_prefill_masked(qf.data_ptr(), kc.data_ptr(), vc.data_ptr(), pad.data_ptr(), fo.data_ptr(), 1, P, H, G,
+                                                    D, T, 0, D ** -0.5, chunk, 1, sink.data_ptr(), gate.data_ptr(), gate.stride(0),
+                                                    vcos.data_ptr(), vsin.data_ptr(), vcos.shape[0], K._stream()), "flash masked")
+        else:
+            L.check(L.lib().jl_flash_prefill(qf.data_ptr(), kc.data_ptr(), vc.data_ptr(), zero.data_ptr(), pad.data_ptr(), fo.data_ptr(),
+                                             1, P, H, G, D, T, 0, D ** -0.5, K._stream()), "flash")
+
+    add("attention in blocks, prompt, bfloat16 and 128-wide heads: the tcgen05 kernel with block bound, sink, gate and turn back",
+        t.kernel(lambda: flash(True)), "the same kernel, plain causal attention (LLaMA path)", t.kernel(lambda: flash(False)),
+        flops=2.0 * H * blk_keys * (D + Dv), like_flops=2.0 * H * (P * (P + 1) / 2) * (D + Dv),
+        note="what Datozen's bfloat16 prompts run at these head sizes; key tiles are 64 wide, so short blocks leave tiles partly masked")
     q1, g1 = qf[:1].contiguous(), gate[:1].contiguous()
     m1 = torch.empty(1, H * Dv, **bf)
     last = torch.full((1,), P - 1, dtype=torch.int32, device=dev)               # the new token closes a block when chunk divides P

@@ -53,7 +53,7 @@ def test_config_round_trip(tmp_path):
     from jax_llama_b200.ops.build import SUBSETS
     sub = registry.kernel_subset("datozen")
     assert "float32" in registry.gpu_dtypes("datozen") and set(SUBSETS[sub]) < set(SUBSETS["hybrid"])
-    assert "seq_token.cu" in SUBSETS[sub] and not {"gla_scan.cu", "delta_scan.cu", "flash_prefill.cu"} & set(SUBSETS[sub])
+    assert "seq_token.cu" in SUBSETS[sub] and not {"gla_scan.cu", "delta_scan.cu", "decode_attn.cu"} & set(SUBSETS[sub])
 
 
 def test_layer_runs_and_defaults():

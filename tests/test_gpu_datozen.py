@@ -436,12 +436,12 @@ A_TOK, B_TOK = 61, 60
 DIM, ROT, WIDTH = 64, 32, 48
 
 
-def _planted_attention(chunk, dtype, seed=5, sink=0.0):
+def _planted_attention(chunk, dtype, seed=5, sink=0.0, dim=DIM, vdim=12, rot=ROT):
     """One layer of attention alone.  Tokens A and B embed as unit vectors and the position rows are zero, so the layer sees
     sqrt(width) times one column of each projection for them.  A's key, in every key/value head, and B's query, in the first
     query head of that group, are the same vector on the unrotated channels: after the head norms their score is
     scale * dim = 24 at any distance, five deviations of a random key's score above zero."""
-    layer = att(heads=4, kv_heads=2, dim=DIM, vdim=12, chunk=chunk, scale=24.0 / DIM, rot=ROT)
+    layer = att(heads=4, kv_heads=2, dim=dim, vdim=vdim, chunk=chunk, scale=24.0 / dim, rot=rot)
     cfg = config([layer], vocab=64, width=WIDTH, side=4)
 
     def tweak(t):
@@ -454,11 +454,11 @@ def _planted_attention(chunk, dtype, seed=5, sink=0.0):
         t[p + "q.norm"].fill_(1.0)
         t[p + "k.norm"].fill_(1.0)
         t[p + "sink"].fill_(sink)
-        u = torch.zeros(DIM, device="cuda")
-        u[ROT:] = torch.randn(DIM - ROT, device="cuda", generator=torch.Generator(device="cuda").manual_seed(3))
+        u = torch.zeros(dim, device="cuda")
+        u[rot:] = torch.randn(dim - rot, device="cuda", generator=torch.Generator(device="cuda").manual_seed(3))
         for c in range(2):
-            t[p + "k"][DIM * c:DIM * (c + 1), 1] = u.to(t[p + "k"].dtype)
-            t[p + "q"][DIM * 2 * c:DIM * (2 * c + 1), 0] = u.to(t[p + "q"].dtype)
+            t[p + "k"][dim * c:dim * (c + 1), 1] = u.to(t[p + "k"].dtype)
+            t[p + "q"][dim * 2 * c:dim * (2 * c + 1), 0] = u.to(t[p + "q"].dtype)
     eng, cpu = build(cfg, dtype, seed=seed, tweak=tweak)
     return cfg, eng, cpu
 
@@ -510,6 +510,28 @@ def test_block_edge_decides(dtype, chunk, where):
     toks[at] = A_TOK
     toks.append(B_TOK)
     _check_last(cfg, eng, cpu, toks, dtype, at, start <= at < n)
+
+
+@pytest.mark.parametrize("chunk", [0, 24, 33, 64, 70, 128, 200])
+@pytest.mark.parametrize("where", ["first_of_block", "last_of_previous", "next", "far_outside", "query_opens_a_block"])
+def test_block_edge_decides_on_the_tensor_core_path(chunk, where):
+    """The same planted key with 128-wide keys and values in bfloat16, where prompts run the tcgen05 kernel: blocks that end
+    inside a key tile or a query tile, three query tiles, the sink and the gate in the kernel's epilogue."""
+    n = 300 if where != "query_opens_a_block" or not chunk else (300 // chunk) * chunk
+    size = chunk or 10 ** 6
+    start = n // size * size
+    at = {"first_of_block": start, "last_of_previous": max(start - 1, 0), "next": n - 1, "far_outside": max(start - 64, 0),
+          "query_opens_a_block": n - 1}[where]
+    at = min(at, n - 1)
+    cfg, eng, cpu = _planted_attention(chunk, torch.bfloat16, sink=22.0, dim=128, vdim=128, rot=64)
+    assert eng.layers[0].mixer._flash_masked_shape()
+    toks = [2 + (i % 50) for i in range(n)]
+    toks[at] = A_TOK
+    toks.append(B_TOK)
+    _check_last(cfg, eng, cpu, toks, torch.bfloat16, at, start <= at < n)
+    want = oracle_logits(cfg, cpu, toks)
+    whole = eng.forward(torch.tensor([toks], device="cuda")).logits[0]
+    assert err(whole, want) < TOL[torch.bfloat16]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
