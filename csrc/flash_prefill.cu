@@ -534,12 +534,19 @@ flash_prefill_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_co
           for (int i = 0; i < 32; ++i) oa[i] = ob[i] = 0u;
         }
         if (row_on) {
+          const float4* c4 = reinterpret_cast<const float4*>(ct + c * 32);   // 16-byte loads: a table row is 256 bytes
+          const float4* s4 = reinterpret_cast<const float4*>(st + c * 32);
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float u = __uint_as_float(oa[i]) * inv, v = __uint_as_float(ob[i]) * inv;
-            const float cs = ct[c * 32 + i], sn = st[c * 32 + i];
-            oa[i] = __float_as_uint(u * cs + v * sn);                 // the turn by -position
-            ob[i] = __float_as_uint(v * cs - u * sn);
+          for (int k = 0; k < 8; ++k) {
+            const float4 cv = __ldg(c4 + k), sv = __ldg(s4 + k);
+            const float cs[4] = {cv.x, cv.y, cv.z, cv.w}, sn[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int i = 4 * k + e;
+              const float u = __uint_as_float(oa[i]) * inv, v = __uint_as_float(ob[i]) * inv;
+              oa[i] = __float_as_uint(u * cs[e] + v * sn[e]);             // the turn by -position
+              ob[i] = __float_as_uint(v * cs[e] - u * sn[e]);
+            }
           }
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
